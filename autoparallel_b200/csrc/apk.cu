@@ -1,0 +1,465 @@
+// Host side of libapk.so: argument checking, TMA descriptor encoding, kernel launches and the
+// symmetric-memory allocator behind the C ABI declared in include/apk.h.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/apk.h"
+#include "gemm_kernel.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+std::atomic<uint64_t> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define APK_CUDA(expr)                                                                          \
+  do {                                                                                          \
+    cudaError_t e__ = (expr);                                                                   \
+    if (e__ != cudaSuccess) return fail(APK_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e__)); \
+  } while (0)
+
+using EncodeFn = PFN_cuTensorMapEncodeTiled_v12000;
+
+// libcuda is reached through the runtime, so the library loads on machines without a driver.
+int get_encode(EncodeFn* out) {
+  static EncodeFn fn = nullptr;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lk(mu);
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    APK_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+    if (q != cudaDriverEntryPointSuccess || p == nullptr) return fail(APK_ERR_CUDA, "cuTensorMapEncodeTiled not found");
+    fn = reinterpret_cast<EncodeFn>(p);
+  }
+  *out = fn;
+  return APK_OK;
+}
+
+// 2-D row-major tensor [rows][cols] with `ld` elements between rows, box [box_rows][box_cols],
+// 128-byte swizzle, out-of-range reads give zeros.
+int encode_2d(CUtensorMap* tm, int dtype, const void* base, uint64_t cols, uint64_t rows, uint64_t ld,
+              uint32_t box_cols, uint32_t box_rows, const char* what) {
+  EncodeFn enc;
+  int rc = get_encode(&enc);
+  if (rc != APK_OK) return rc;
+  const uint64_t es = (dtype == APK_BF16) ? 2 : 1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return fail(APK_ERR_ARG, "%s: base pointer must be 16-byte aligned", what);
+  if ((ld * es) % 16 != 0) return fail(APK_ERR_ARG, "%s: row pitch (%llu bytes) must be a multiple of 16", what, (unsigned long long)(ld * es));
+  if (box_cols * es != apk::ROW_BYTES) return fail(APK_ERR_ARG, "%s: inner box must span 128 bytes", what);
+  if (box_rows > 256) return fail(APK_ERR_ARG, "%s: box rows > 256", what);
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * es};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, dtype == APK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(APK_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed with %d", what, (int)r);
+  return APK_OK;
+}
+
+struct DeviceInfo {
+  int sms = 0;
+  int clock_khz = 0;
+  bool ok = false;
+};
+
+int device_info(DeviceInfo* out) {
+  static DeviceInfo cache[64];
+  int dev = 0;
+  APK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(APK_ERR_ARG, "device index %d out of range", dev);
+  if (!cache[dev].ok) {
+    int major = 0;
+    APK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (major != 10) return fail(APK_ERR_CUDA, "device %d has compute capability %d.x; this library needs sm_100", dev, major);
+    APK_CUDA(cudaDeviceGetAttribute(&cache[dev].sms, cudaDevAttrMultiProcessorCount, dev));
+    APK_CUDA(cudaDeviceGetAttribute(&cache[dev].clock_khz, cudaDevAttrClockRate, dev));
+    cache[dev].ok = true;
+  }
+  *out = cache[dev];
+  return APK_OK;
+}
+
+template <int BN, int STAGES, bool FP8>
+int launch_instance(const apk::KParams& kp, int grid, cudaStream_t stream) {
+  using L = apk::SmemLayout<BN, STAGES>;
+  auto kern = apk::gemm_fused_kernel<BN, STAGES, FP8>;
+  static bool configured[64] = {};
+  int dev = 0;
+  APK_CUDA(cudaGetDevice(&dev));
+  if (!configured[dev]) {
+    APK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+    configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(apk::NUM_THREADS);
+  cfg.dynamicSmemBytes = L::TOTAL;
+  cfg.stream = stream;
+  // Cooperative: all CTAs must be resident at once, because the communication warps of every
+  // CTA feed row blocks that other CTAs' producers wait for.
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  APK_CUDA(cudaLaunchKernelEx(&cfg, kern, kp));
+  g_launches.fetch_add(1);
+  return APK_OK;
+}
+
+int launch(const apk::KParams& kp, int max_n, bool fp8, cudaStream_t stream) {
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc != APK_OK) return rc;
+  const bool narrow = max_n <= 128;
+  const int bn = narrow ? 128 : 256;
+  long long nt = 0;
+  for (int b = 0; b < kp.nB; ++b) nt += (kp.N[b] + bn - 1) / bn;
+  const long long mt = (kp.rows_per_rank + apk::BM - 1) / apk::BM;
+  const long long tiles = nt * mt * (kp.mode == apk::MODE_PLAIN ? 1 : kp.ws);
+  if (tiles <= 0) return APK_OK;
+  if (tiles > 0x7fffffffLL) return fail(APK_ERR_ARG, "too many tiles");
+  const int grid = (int)(tiles < di.sms ? tiles : di.sms);
+  if (narrow) {
+    return fp8 ? launch_instance<128, 6, true>(kp, grid, stream) : launch_instance<128, 6, false>(kp, grid, stream);
+  }
+  return fp8 ? launch_instance<256, 4, true>(kp, grid, stream) : launch_instance<256, 4, false>(kp, grid, stream);
+}
+
+uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
+
+int fill_operand(apk::KParams* kp, int b, const apk_operand& op, int dtype, int K, int bn, const char* what) {
+  if (op.B == nullptr || op.out == nullptr) return fail(APK_ERR_ARG, "%s: null B or out", what);
+  if (op.N <= 0) return fail(APK_ERR_ARG, "%s: N must be positive", what);
+  if (op.out_dtype != APK_BF16 && op.out_dtype != APK_F32) return fail(APK_ERR_ARG, "%s: out dtype must be bf16 or f32", what);
+  const int oes = op.out_dtype == APK_F32 ? 4 : 2;
+  const int vec = 16 / oes;
+  if (op.N % vec != 0) return fail(APK_ERR_ARG, "%s: N (%d) must be a multiple of %d", what, op.N, vec);
+  if ((reinterpret_cast<uintptr_t>(op.out) & 15u) != 0 || (op.ldo * oes) % 16 != 0)
+    return fail(APK_ERR_ARG, "%s: output must be 16-byte aligned with a 16-byte multiple pitch", what);
+  const int bke = dtype == APK_BF16 ? 64 : 128;
+  int rc;
+  if (op.n_major) {
+    rc = encode_2d(&kp->tmB[b], dtype, op.B, (uint64_t)op.N, (uint64_t)K, (uint64_t)op.ldb, bke, bke, what);
+  } else {
+    rc = encode_2d(&kp->tmB[b], dtype, op.B, (uint64_t)K, (uint64_t)op.N, (uint64_t)op.ldb, bke, bn, what);
+  }
+  if (rc != APK_OK) return rc;
+  kp->N[b] = op.N;
+  kp->b_nmajor[b] = op.n_major ? 1 : 0;
+  kp->out[b] = op.out;
+  kp->ldo[b] = op.ldo;
+  kp->out_fp32[b] = op.out_dtype == APK_F32;
+  if (op.b_scale_mode != APK_SCALE_NONE && op.b_scale_mode != APK_SCALE_SCALAR && op.b_scale_mode != APK_SCALE_VECTOR)
+    return fail(APK_ERR_ARG, "%s: bad b_scale_mode", what);
+  if (op.b_scale_mode != APK_SCALE_NONE && op.b_scale == nullptr) return fail(APK_ERR_ARG, "%s: b_scale is null", what);
+  kp->b_scale[b] = op.b_scale;
+  kp->b_scale_mode[b] = op.b_scale_mode;
+  kp->bias[b] = op.bias;
+  kp->bias_fp32[b] = op.bias_dtype == APK_F32;
+  kp->result_scale[b] = op.result_scale;
+  return APK_OK;
+}
+
+int check_comm(const apk_comm* c) {
+  if (c == nullptr) return fail(APK_ERR_ARG, "comm is null");
+  if (c->world < 1 || c->world > APK_MAX_WORLD) return fail(APK_ERR_ARG, "world must be in [1, %d]", APK_MAX_WORLD);
+  if (c->rank < 0 || c->rank >= c->world) return fail(APK_ERR_ARG, "rank out of range");
+  if (c->status == nullptr) return fail(APK_ERR_ARG, "comm.status is null");
+  if (c->world > 1) {
+    for (int r = 0; r < c->world; ++r) {
+      if (c->data[r] == nullptr || c->flags[r] == nullptr) return fail(APK_ERR_ARG, "comm.data/flags[%d] is null", r);
+    }
+    if (c->flag_bytes < 8192) return fail(APK_ERR_SIZE, "signal pad too small");
+    if (c->ctrl == nullptr) return fail(APK_ERR_ARG, "comm.ctrl is null");
+  }
+  return APK_OK;
+}
+
+long long timeout_cycles(const apk_comm* c, const DeviceInfo& di) {
+  double s = c->timeout_s > 0 ? c->timeout_s : 30.0;
+  return (long long)(s * 1e3 * (double)di.clock_khz);
+}
+
+constexpr uint64_t kFlagRsOffset = 4096;  // bytes: staged flags live below, per-tile flags above
+
+}  // namespace
+
+extern "C" {
+
+int apk_abi_version(void) { return APK_ABI_VERSION; }
+const char* apk_last_error(void) { return g_err; }
+uint64_t apk_launch_count(void) { return g_launches.load(); }
+
+int apk_symm_alloc(uint64_t bytes, void** ptr) {
+  if (ptr == nullptr || bytes == 0) return fail(APK_ERR_ARG, "apk_symm_alloc: bad arguments");
+  void* p = nullptr;
+  APK_CUDA(cudaMalloc(&p, bytes));
+  cudaError_t e = cudaMemset(p, 0, bytes);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return fail(APK_ERR_CUDA, "cudaMemset: %s", cudaGetErrorString(e));
+  }
+  APK_CUDA(cudaDeviceSynchronize());
+  *ptr = p;
+  return APK_OK;
+}
+
+int apk_symm_free(void* ptr) {
+  if (ptr == nullptr) return APK_OK;
+  APK_CUDA(cudaFree(ptr));
+  return APK_OK;
+}
+
+int apk_symm_export(const void* ptr, uint8_t handle[64]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
+  if (ptr == nullptr || handle == nullptr) return fail(APK_ERR_ARG, "apk_symm_export: null argument");
+  cudaIpcMemHandle_t h;
+  APK_CUDA(cudaIpcGetMemHandle(&h, const_cast<void*>(ptr)));
+  memcpy(handle, &h, 64);
+  return APK_OK;
+}
+
+int apk_symm_import(const uint8_t handle[64], void** ptr) {
+  if (ptr == nullptr || handle == nullptr) return fail(APK_ERR_ARG, "apk_symm_import: null argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  void* p = nullptr;
+  APK_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  *ptr = p;
+  return APK_OK;
+}
+
+int apk_symm_unimport(void* ptr) {
+  if (ptr == nullptr) return APK_OK;
+  APK_CUDA(cudaIpcCloseMemHandle(ptr));
+  return APK_OK;
+}
+
+uint64_t apk_ag_gemm_arena_bytes(const apk_ag_gemm_args* a, int32_t world) {
+  if (a == nullptr || world <= 1) return 0;
+  const uint64_t es = a->dtype == APK_BF16 ? 2 : 1;
+  uint64_t bytes = align_up((uint64_t)a->rows_per_rank * (uint64_t)a->K * es, 256);
+  if (a->a_scale_mode == APK_SCALE_VECTOR) bytes += align_up((uint64_t)a->rows_per_rank * 4, 256);
+  return bytes;
+}
+
+uint64_t apk_gemm_rs_arena_bytes(const apk_gemm_rs_args* a, int32_t world) {
+  if (a == nullptr || world <= 1) return 0;
+  const uint64_t oes = a->B.out_dtype == APK_F32 ? 4 : 2;
+  return align_up((uint64_t)a->M * (uint64_t)a->B.N * oes, 256);
+}
+
+uint64_t apk_ctrl_bytes(int32_t rows_per_rank, int32_t world) {
+  const uint64_t mt = ((uint64_t)rows_per_rank + apk::BM - 1) / apk::BM;
+  return 256 + 4 * mt * (uint64_t)(world < 1 ? 1 : world);
+}
+
+int apk_ag_gemm(const apk_comm* comm, const apk_ag_gemm_args* a, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  int rc = check_comm(comm);
+  if (rc != APK_OK) return rc;
+  if (a == nullptr) return fail(APK_ERR_ARG, "args is null");
+  if (a->dtype != APK_BF16 && a->dtype != APK_E4M3) return fail(APK_ERR_ARG, "dtype must be bf16 or e4m3");
+  if (a->nB < 1 || a->nB > APK_MAX_B) return fail(APK_ERR_ARG, "nB must be in [1, %d]", APK_MAX_B);
+  if (a->rows_per_rank < 0 || a->K <= 0) return fail(APK_ERR_ARG, "bad shape");
+  if (a->rows_per_rank == 0) return APK_OK;
+  if (a->A_shard == nullptr) return fail(APK_ERR_ARG, "A_shard is null");
+  const int ws = comm->world;
+  const int es = a->dtype == APK_BF16 ? 2 : 1;
+  const int64_t M = (int64_t)a->rows_per_rank * ws;
+  if (M > 0x7fffffffLL) return fail(APK_ERR_ARG, "M too large");
+  const bool need_gathered = ws > 1 || a->return_A;
+  if (need_gathered && a->A_gathered == nullptr) return fail(APK_ERR_ARG, "A_gathered is required");
+  if (((int64_t)a->K * es) % 16 != 0) return fail(APK_ERR_ARG, "K * element size must be a multiple of 16 bytes");
+  DeviceInfo di;
+  rc = device_info(&di);
+  if (rc != APK_OK) return rc;
+
+  apk::KParams kp;
+  memset(&kp, 0, sizeof(kp));
+  kp.mode = apk::MODE_AG;
+  kp.ws = ws;
+  kp.rank = comm->rank;
+  kp.nB = a->nB;
+  kp.M = (int32_t)M;
+  kp.K = a->K;
+  kp.rows_per_rank = a->rows_per_rank;
+  kp.elem_bytes = es;
+  int max_n = 0;
+  for (int b = 0; b < a->nB; ++b) max_n = a->Bs[b].N > max_n ? a->Bs[b].N : max_n;
+  const int bn = max_n <= 128 ? 128 : 256;
+  const int bke = a->dtype == APK_BF16 ? 64 : 128;
+  rc = encode_2d(&kp.tmA0, a->dtype, a->A_shard, (uint64_t)a->K, (uint64_t)a->rows_per_rank, (uint64_t)a->lda, bke, apk::BM, "A_shard");
+  if (rc != APK_OK) return rc;
+  if (need_gathered) {
+    rc = encode_2d(&kp.tmA1, a->dtype, a->A_gathered, (uint64_t)a->K, (uint64_t)M, (uint64_t)a->K, bke, apk::BM, "A_gathered");
+    if (rc != APK_OK) return rc;
+  }
+  for (int b = 0; b < a->nB; ++b) {
+    rc = fill_operand(&kp, b, a->Bs[b], a->dtype, a->K, bn, "Bs[i]");
+    if (rc != APK_OK) return rc;
+  }
+  // A scale
+  switch (a->a_scale_mode) {
+    case APK_SCALE_NONE:
+      break;
+    case APK_SCALE_SCALAR:
+      kp.a_scale_mode = 1;
+      kp.a_scale_full = a->A_scale;
+      break;
+    case APK_SCALE_VECTOR:
+      kp.a_scale_mode = 2;
+      kp.a_scale_own = a->A_scale;
+      if (ws > 1 && a->A_scale_gathered == nullptr) return fail(APK_ERR_ARG, "A_scale_gathered is required");
+      kp.ag_has_scale = ws > 1;
+      kp.ag_scale_src = a->A_scale;
+      kp.ag_scale_gathered = a->A_scale_gathered;
+      break;
+    case APK_SCALE_ROWS_REPLICATED:
+      kp.a_scale_mode = 2;
+      kp.a_scale_full = a->A_scale;
+      break;
+    default:
+      return fail(APK_ERR_ARG, "bad a_scale_mode");
+  }
+  if (a->a_scale_mode != APK_SCALE_NONE && a->A_scale == nullptr) return fail(APK_ERR_ARG, "A_scale is null");
+
+  kp.ag_src = reinterpret_cast<const uint8_t*>(a->A_shard);
+  kp.ag_chunk_bytes = (int64_t)a->rows_per_rank * a->K * es;
+  kp.ag_gathered = reinterpret_cast<uint8_t*>(a->A_gathered);
+  kp.ag_copy_own = a->return_A ? 1 : 0;
+  if ((ws > 1 || a->return_A) && a->lda != a->K) return fail(APK_ERR_ARG, "A_shard must be contiguous (lda == K)");
+  kp.ag_scale_off = (int64_t)align_up((uint64_t)kp.ag_chunk_bytes, 256);
+  kp.epoch = comm->epoch;
+  kp.status = comm->status;
+  kp.timeout_cycles = timeout_cycles(comm, di);
+  kp.reduce_scale = 1.0f;
+  const uint64_t ctrl_need = apk_ctrl_bytes(a->rows_per_rank, ws);
+  if (ws > 1) {
+    const uint64_t half = comm->data_bytes / 2;
+    const uint64_t need = apk_ag_gemm_arena_bytes(a, ws);
+    if (need > half) return fail(APK_ERR_SIZE, "all-gather staging needs %llu bytes per half, arena has %llu", (unsigned long long)need, (unsigned long long)half);
+    if (ctrl_need > comm->ctrl_bytes) return fail(APK_ERR_SIZE, "ctrl scratch too small");
+    const uint64_t off = (comm->epoch & 1u) ? half : 0;
+    for (int r = 0; r < ws; ++r) {
+      kp.ag_symm_peer[r] = reinterpret_cast<const uint8_t*>(comm->data[r]) + off;
+      kp.staged_peer[r] = reinterpret_cast<uint32_t*>(comm->flags[r]);
+    }
+    kp.ag_symm_local = reinterpret_cast<uint8_t*>(comm->data[comm->rank]) + off;
+    kp.staged_local = reinterpret_cast<uint32_t*>(comm->flags[comm->rank]);
+    kp.ctrl = reinterpret_cast<uint32_t*>(comm->ctrl);
+    kp.ready = kp.ctrl + 64;
+    APK_CUDA(cudaMemsetAsync(comm->ctrl, 0, ctrl_need, stream));
+  }
+  return launch(kp, max_n, a->dtype == APK_E4M3, stream);
+}
+
+int apk_gemm_rs(const apk_comm* comm, const apk_gemm_rs_args* a, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  int rc = check_comm(comm);
+  if (rc != APK_OK) return rc;
+  if (a == nullptr) return fail(APK_ERR_ARG, "args is null");
+  if (a->dtype != APK_BF16 && a->dtype != APK_E4M3) return fail(APK_ERR_ARG, "dtype must be bf16 or e4m3");
+  const int ws = comm->world;
+  if (a->M < 0 || a->K <= 0) return fail(APK_ERR_ARG, "bad shape");
+  if (a->M % ws != 0) return fail(APK_ERR_ARG, "M (%d) must be divisible by the group size (%d)", a->M, ws);
+  if (a->M == 0) return APK_OK;
+  if (a->A == nullptr) return fail(APK_ERR_ARG, "A is null");
+  if (a->reduce_op != APK_REDUCE_SUM && a->reduce_op != APK_REDUCE_AVG) return fail(APK_ERR_ARG, "reduce_op must be sum or avg");
+  const int es = a->dtype == APK_BF16 ? 2 : 1;
+  if (((int64_t)a->K * es) % 16 != 0) return fail(APK_ERR_ARG, "K * element size must be a multiple of 16 bytes");
+  DeviceInfo di;
+  rc = device_info(&di);
+  if (rc != APK_OK) return rc;
+
+  apk::KParams kp;
+  memset(&kp, 0, sizeof(kp));
+  kp.mode = apk::MODE_RS;
+  kp.ws = ws;
+  kp.rank = comm->rank;
+  kp.nB = 1;
+  kp.M = a->M;
+  kp.K = a->K;
+  kp.rows_per_rank = a->M / ws;
+  kp.elem_bytes = es;
+  const int bn = a->B.N <= 128 ? 128 : 256;
+  const int bke = a->dtype == APK_BF16 ? 64 : 128;
+  rc = encode_2d(&kp.tmA0, a->dtype, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, bke, apk::BM, "A");
+  if (rc != APK_OK) return rc;
+  rc = fill_operand(&kp, 0, a->B, a->dtype, a->K, bn, "B");
+  if (rc != APK_OK) return rc;
+  switch (a->a_scale_mode) {
+    case APK_SCALE_NONE:
+      break;
+    case APK_SCALE_SCALAR:
+      kp.a_scale_mode = 1;
+      kp.a_scale_full = a->A_scale;
+      break;
+    case APK_SCALE_VECTOR:
+    case APK_SCALE_ROWS_REPLICATED:
+      kp.a_scale_mode = 2;
+      kp.a_scale_full = a->A_scale;
+      break;
+    default:
+      return fail(APK_ERR_ARG, "bad a_scale_mode");
+  }
+  if (a->a_scale_mode != APK_SCALE_NONE && a->A_scale == nullptr) return fail(APK_ERR_ARG, "A_scale is null");
+  kp.reduce_scale = a->reduce_op == APK_REDUCE_AVG ? 1.0f / (float)ws : 1.0f;
+  kp.epoch = comm->epoch;
+  kp.status = comm->status;
+  kp.timeout_cycles = timeout_cycles(comm, di);
+  if (ws > 1) {
+    const uint64_t half = comm->data_bytes / 2;
+    const uint64_t need = apk_gemm_rs_arena_bytes(a, ws);
+    if (need > half) return fail(APK_ERR_SIZE, "reduce-scatter arena needs %llu bytes per half, arena has %llu", (unsigned long long)need, (unsigned long long)half);
+    const uint64_t max_tiles = (comm->flag_bytes - kFlagRsOffset) / 4 / (uint64_t)ws;
+    const uint64_t tiles = (uint64_t)((kp.rows_per_rank + apk::BM - 1) / apk::BM) * (uint64_t)((a->B.N + bn - 1) / bn);
+    if (tiles > max_tiles) return fail(APK_ERR_SIZE, "signal pad holds %llu tile flags per rank, need %llu", (unsigned long long)max_tiles, (unsigned long long)tiles);
+    kp.rs_max_tiles = (int32_t)max_tiles;
+    const uint64_t off = (comm->epoch & 1u) ? half : 0;
+    for (int r = 0; r < ws; ++r) {
+      kp.rs_arena_peer[r] = reinterpret_cast<uint8_t*>(comm->data[r]) + off;
+      kp.rs_flag_peer[r] = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(comm->flags[r]) + kFlagRsOffset);
+    }
+    kp.rs_arena_local = kp.rs_arena_peer[comm->rank];
+    kp.rs_flag_local = kp.rs_flag_peer[comm->rank];
+  }
+  return launch(kp, a->B.N, a->dtype == APK_E4M3, stream);
+}
+
+int apk_check_status(const apk_comm* comm, void* stream_, uint32_t* raw) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (comm == nullptr || comm->status == nullptr) return fail(APK_ERR_ARG, "comm.status is null");
+  uint32_t v = 0;
+  APK_CUDA(cudaMemcpyAsync(&v, comm->status, 4, cudaMemcpyDeviceToHost, stream));
+  APK_CUDA(cudaStreamSynchronize(stream));
+  if (raw != nullptr) *raw = v;
+  if (v != 0) {
+    APK_CUDA(cudaMemsetAsync(comm->status, 0, 4, stream));
+    APK_CUDA(cudaStreamSynchronize(stream));
+    static const char* names[] = {"ok", "pipeline mbarrier", "peer 'staged' flag", "gathered rows", "peer partial"};
+    const uint32_t code = v & 0xffu;
+    return fail(APK_ERR_TIMEOUT, "device wait timed out: %s (detail %u)", code < 5 ? names[code] : "?", v >> 8);
+  }
+  return APK_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,686 @@
+// Persistent tcgen05/TMEM GEMM for sm_100a with the two async-TP fusions built in.
+//
+// One CTA per SM, 10 warps:
+//   warp 0      TMA producer: waits for the rows of A it needs to be present in local
+//               memory (all-gather mode), then streams A/B tiles into a shared-memory ring.
+//   warp 1      MMA issuer: one thread issues tcgen05.mma into a double-buffered TMEM
+//               accumulator (2 x BN fp32 columns).
+//   warps 2-5   epilogue: tcgen05.ld -> scale/bias/convert -> global. In reduce-scatter mode
+//               tiles owned by another rank are written straight into that rank's staging
+//               arena over NVLink and its per-tile flag is released; tiles owned by this rank
+//               are computed last and summed with the partials that arrived from the peers.
+//   warps 6-9   communication (all-gather mode): stage the local shard in the symmetric
+//               buffer, tell the peers, then pull every peer's shard in ring order
+//               (rank+1, rank+2, ...) into the local gathered-A buffer in 4 KiB pieces,
+//               bumping a per-row-block counter the producer waits on.
+//
+// The role of each chunk of rows follows the schedule of the reference's pipelines
+// (autoparallel/asynctp_ops.py:153-164 for all-gather: own shard first, then rank+step;
+// :250-321 for reduce-scatter: destination rank+step, own chunk last).
+//
+// Every wait (mbarrier, flag, counter) is bounded by a cycle budget; when it runs out the
+// kernel records a code in the status word, raises a CTA-wide abort flag, drains its own
+// copies, frees TMEM and returns.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace apk {
+
+constexpr int BM = 128;             // rows per tile = TMEM lanes
+constexpr int ROW_BYTES = 128;      // bytes per shared-memory row = TMA inner box = swizzle span
+constexpr int MAX_B = 4;            // weight matrices sharing one gathered A
+constexpr int MAX_WORLD = 8;
+constexpr int EPI_WARPS = 4;
+constexpr int COMM_WARPS = 4;
+constexpr int NUM_THREADS = 32 * (2 + EPI_WARPS + COMM_WARPS);
+constexpr int PIECE_BYTES = 4096;   // unit of the all-gather pull: 32 lanes x 16 B x 8
+constexpr int FLAG_STRIDE = 32;     // u32 words between two ranks' "staged" flags (128 B)
+
+enum Mode : int32_t { MODE_PLAIN = 0, MODE_AG = 1, MODE_RS = 2 };
+
+// Status codes written (first one wins) to the status word when a wait gives up.
+enum Status : uint32_t {
+  ST_OK = 0,
+  ST_TIMEOUT_MBAR = 1,       // a pipeline mbarrier never completed
+  ST_TIMEOUT_STAGED = 2,     // a peer never announced its staged shard
+  ST_TIMEOUT_READY = 3,      // rows of a gathered chunk never arrived locally
+  ST_TIMEOUT_PARTIAL = 4,    // a peer's reduce-scatter partial never arrived
+};
+
+struct alignas(64) KParams {
+  CUtensorMap tmA0;            // plain / RS: all of A. AG: the local shard [rows_per_rank, K]
+  CUtensorMap tmA1;            // AG: the gathered A [M, K]
+  CUtensorMap tmB[MAX_B];
+  int32_t mode, ws, rank, nB;
+  int32_t M, K, rows_per_rank, elem_bytes;
+  int32_t N[MAX_B];
+  int32_t b_nmajor[MAX_B];     // 1: B is [K][N] with N contiguous; 0: K contiguous
+  void* out[MAX_B];
+  int64_t ldo[MAX_B];
+  int32_t out_fp32[MAX_B];
+  // ---- scaled (fp8) epilogue
+  int32_t a_scale_mode;        // 0 none, 1 one scalar, 2 one per row
+  const float* a_scale_own;    // AG row-wise-sharded: scales of the local shard's rows
+  const float* a_scale_full;   // scalar, or per-row indexed by the global row
+  const float* b_scale[MAX_B];
+  int32_t b_scale_mode[MAX_B]; // 0 none, 1 scalar, 2 per column
+  const void* bias[MAX_B];     // per column, nullable
+  int32_t bias_fp32[MAX_B];
+  const float* result_scale[MAX_B];
+  // ---- all-gather
+  const uint8_t* ag_src;               // local shard bytes
+  uint8_t* ag_symm_local;              // this rank's symmetric staging buffer (current parity)
+  const uint8_t* ag_symm_peer[MAX_WORLD];
+  uint8_t* ag_gathered;                // [M, K]
+  int32_t ag_copy_own;                 // also place the local shard in ag_gathered
+  int32_t ag_has_scale;
+  int64_t ag_chunk_bytes;              // rows_per_rank * K * elem_bytes
+  int64_t ag_scale_off;                // offset of the row scales inside the symmetric buffer
+  const float* ag_scale_src;
+  float* ag_scale_gathered;            // [M]
+  uint32_t* staged_local;              // [ws * FLAG_STRIDE] in this rank's signal pad
+  uint32_t* staged_peer[MAX_WORLD];
+  uint32_t* ready;                     // [ws * tiles_m_per_chunk] local counters, zeroed per call
+  uint32_t* ctrl;                      // local scratch counters, zeroed per call
+  // ---- reduce-scatter
+  uint8_t* rs_arena_local;             // [ws][rows_per_rank][N] partials (current parity)
+  uint8_t* rs_arena_peer[MAX_WORLD];
+  uint32_t* rs_flag_local;             // [ws][rs_max_tiles]
+  uint32_t* rs_flag_peer[MAX_WORLD];
+  int32_t rs_max_tiles;
+  float reduce_scale;                  // 1 for sum, 1/ws for avg
+  // ---- common
+  uint32_t epoch;
+  uint32_t* status;
+  long long timeout_cycles;
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * ROW_BYTES;
+  static constexpr int B_BYTES = BN * ROW_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 5;
+  static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
+  static constexpr int TOTAL = MISC_OFF + 16 + 1024;  // + alignment slack
+};
+
+struct TileInfo {
+  int chunk;        // which rank's rows (AG: source rank, RS: destination rank)
+  int mt;           // row block inside the chunk
+  int b;            // which B / output
+  int n0;           // first column inside output b
+  int tile_in_chunk;
+  int rows_valid;   // rows of this tile that exist
+  int n_valid;      // columns of this tile that exist
+};
+
+struct Sched {
+  int nt_b[MAX_B];
+  int nt_total;
+  int mt_per_chunk;
+  int tiles_per_chunk;
+  int num_chunks;
+  int total_tiles;
+};
+
+template <int BN>
+__device__ __forceinline__ Sched make_sched(const KParams& p) {
+  Sched s;
+  s.nt_total = 0;
+#pragma unroll
+  for (int b = 0; b < MAX_B; ++b) {
+    s.nt_b[b] = (b < p.nB) ? (p.N[b] + BN - 1) / BN : 0;
+    s.nt_total += s.nt_b[b];
+  }
+  s.mt_per_chunk = (p.rows_per_rank + BM - 1) / BM;
+  s.tiles_per_chunk = s.mt_per_chunk * s.nt_total;
+  s.num_chunks = (p.mode == MODE_PLAIN) ? 1 : p.ws;
+  s.total_tiles = s.tiles_per_chunk * s.num_chunks;
+  return s;
+}
+
+template <int BN>
+__device__ __forceinline__ TileInfo decode_tile(const KParams& p, const Sched& s, int t) {
+  TileInfo ti;
+  const int step = t / s.tiles_per_chunk;
+  int r = t - step * s.tiles_per_chunk;
+  if (p.mode == MODE_AG) {
+    ti.chunk = (p.rank + step) % p.ws;
+  } else if (p.mode == MODE_RS) {
+    ti.chunk = (p.rank + 1 + step) % p.ws;
+  } else {
+    ti.chunk = 0;
+  }
+  ti.mt = r / s.nt_total;
+  int nt = r - ti.mt * s.nt_total;
+  ti.tile_in_chunk = r;
+  ti.b = 0;
+#pragma unroll
+  for (int b = 0; b < MAX_B - 1; ++b) {
+    if (ti.b == b && nt >= s.nt_b[b]) {
+      nt -= s.nt_b[b];
+      ti.b = b + 1;
+    }
+  }
+  ti.n0 = nt * BN;
+  ti.rows_valid = min(BM, p.rows_per_rank - ti.mt * BM);
+  ti.n_valid = min(BN, p.N[ti.b] - ti.n0);
+  return ti;
+}
+
+// Number of 4 KiB pieces the all-gather pull splits row block `mt` of a chunk into.
+__device__ __forceinline__ int ag_tile_pieces(const KParams& p, int mt) {
+  const long long tile_bytes = (long long)BM * p.K * p.elem_bytes;
+  const long long start = (long long)mt * tile_bytes;
+  long long len = p.ag_chunk_bytes - start;
+  if (len > tile_bytes) len = tile_bytes;
+  return (int)((len + PIECE_BYTES - 1) / PIECE_BYTES);
+}
+
+__device__ __forceinline__ void set_status(const KParams& p, uint32_t code, uint32_t detail) {
+  atomicCAS(p.status, 0u, code | (detail << 8));
+}
+
+// Bounded mbarrier wait. Returns false when the wait was abandoned.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const KParams& p, volatile uint32_t* abort_flag) {
+  uint32_t spins = 0;
+  long long t0 = 0;
+  while (!ptx::mbar_try_wait(bar, parity)) {
+    if ((++spins & 0xffu) == 0) {
+      if (*abort_flag) return false;
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > p.timeout_cycles) {
+        set_status(p, ST_TIMEOUT_MBAR, bar & 0xffffu);
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// Bounded wait until the u32 at `flag` has reached `target` (wrap-safe). `sys` selects the scope.
+template <bool SYS>
+__device__ __forceinline__ bool flag_wait(const uint32_t* flag, uint32_t target, const KParams& p,
+                                          volatile uint32_t* abort_flag, uint32_t code, uint32_t detail) {
+  uint32_t spins = 0;
+  long long t0 = 0;
+  while (true) {
+    const uint32_t v = SYS ? ptx::ld_acquire_sys(flag) : ptx::ld_acquire_gpu(flag);
+    if ((int32_t)(v - target) >= 0) return true;
+    if ((++spins & 0x3fu) == 0) {
+      if (*abort_flag) return false;
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > p.timeout_cycles) {
+        set_status(p, code, detail);
+        *abort_flag = 1;
+        return false;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Writes `nvalid` (multiple of 8 for bf16, 4 for fp32; <= 32) consecutive outputs of one row.
+__device__ __forceinline__ void store_row32(void* dst, const float (&v)[32], int nvalid, bool fp32) {
+  if (fp32) {
+    float4* d = reinterpret_cast<float4*>(dst);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (j * 4 < nvalid) d[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    }
+  } else {
+    uint4* d = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j * 8 < nvalid) {
+        uint4 q;
+        q.x = pack_bf16(v[8 * j + 0], v[8 * j + 1]);
+        q.y = pack_bf16(v[8 * j + 2], v[8 * j + 3]);
+        q.z = pack_bf16(v[8 * j + 4], v[8 * j + 5]);
+        q.w = pack_bf16(v[8 * j + 6], v[8 * j + 7]);
+        d[j] = q;
+      }
+    }
+  }
+}
+
+// v += the 32 values of one row of a partial that a peer left in the local arena.
+__device__ __forceinline__ void add_row32(const void* src, float (&v)[32], int nvalid, bool fp32) {
+  if (fp32) {
+    const float4* s = reinterpret_cast<const float4*>(src);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (j * 4 < nvalid) {
+        const float4 q = __ldcg(s + j);
+        v[4 * j] += q.x; v[4 * j + 1] += q.y; v[4 * j + 2] += q.z; v[4 * j + 3] += q.w;
+      }
+    }
+  } else {
+    const uint4* s = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j * 8 < nvalid) {
+        const uint4 q = __ldcg(s + j);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          v[8 * j + 2 * e] += __uint_as_float(w[e] << 16);
+          v[8 * j + 2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+        }
+      }
+    }
+  }
+}
+
+// One warp copies up to 4 KiB (n16 16-byte words) src -> dst (and dst2 when given).
+template <bool PEER>
+__device__ __forceinline__ void copy_piece(const uint8_t* src, uint8_t* dst, uint8_t* dst2, int n16, int lane) {
+  uint4 r[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const int i = u * 32 + lane;
+    if (i < n16) {
+      r[u] = PEER ? ptx::ld_relaxed_sys_v4(src + (size_t)i * 16) : __ldcg(reinterpret_cast<const uint4*>(src) + i);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const int i = u * 32 + lane;
+    if (i < n16) {
+      reinterpret_cast<uint4*>(dst)[i] = r[u];
+      if (dst2 != nullptr) reinterpret_cast<uint4*>(dst2)[i] = r[u];
+    }
+  }
+}
+
+template <int BN, int STAGES, bool FP8>
+__global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid_constant__ KParams p) {
+  using L = SmemLayout<BN, STAGES>;
+  constexpr int BKE = FP8 ? 128 : 64;           // K elements per stage (128 bytes)
+  constexpr int UMMA_K = FP8 ? 32 : 16;         // K elements per tcgen05.mma (32 bytes)
+  constexpr int KSTEPS = BKE / UMMA_K;          // 4
+  constexpr int NPB = FP8 ? 128 : 64;           // N elements per TMA box when B is N-major
+  constexpr uint32_t TMEM_COLS = 2 * BN <= 32 ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = ptx::smem_u32(smem);
+  const uint32_t bar_base = smem_base + L::BAR_OFF;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 4);
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + L::MISC_OFF);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFF + 4);
+  volatile uint32_t* epi_verdict = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFF + 8);  // [2]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const Sched sched = make_sched<BN>(p);
+  const int num_kb = (p.K + BKE - 1) / BKE;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), EPI_WARPS);
+    }
+    ptx::mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_ptr_smem), TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp == 0) {
+    // ============================================================ TMA producer
+    if (lane == 0) {
+      ptx::tma_prefetch_desc(&p.tmA0);
+      if (p.mode == MODE_AG) ptx::tma_prefetch_desc(&p.tmA1);
+      for (int b = 0; b < p.nB; ++b) ptx::tma_prefetch_desc(&p.tmB[b]);
+      uint32_t it = 0;       // k-block counter over the CTA's lifetime
+      bool ok = true;
+      for (int t = blockIdx.x; t < sched.total_tiles && ok; t += gridDim.x) {
+        const TileInfo ti = decode_tile<BN>(p, sched, t);
+        const CUtensorMap* tmA = &p.tmA0;
+        int arow = ti.mt * BM;
+        if (p.mode == MODE_AG && ti.chunk != p.rank) {
+          tmA = &p.tmA1;
+          arow += ti.chunk * p.rows_per_rank;
+          const uint32_t expect = (uint32_t)ag_tile_pieces(p, ti.mt) + (p.ag_has_scale ? 1u : 0u);
+          ok = flag_wait<false>(p.ready + ti.chunk * sched.mt_per_chunk + ti.mt, expect, p, abort_flag,
+                                ST_TIMEOUT_READY, (uint32_t)ti.chunk);
+          if (!ok) break;
+          ptx::fence_proxy_async_global();
+        } else if (p.mode == MODE_RS) {
+          arow += ti.chunk * p.rows_per_rank;
+        }
+        const bool nmajor = p.b_nmajor[ti.b] != 0;
+        const CUtensorMap* tmB = &p.tmB[ti.b];
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          ok = mbar_wait(empty_bar(s), ph ^ 1u, p, abort_flag);
+          if (!ok) break;
+          const uint32_t a_dst = smem_base + s * L::STAGE_BYTES;
+          const uint32_t b_dst = a_dst + L::A_BYTES;
+          ptx::mbar_expect_tx(full_bar(s), L::STAGE_BYTES);
+          ptx::tma_load_2d(a_dst, tmA, full_bar(s), kb * BKE, arow);
+          if (!nmajor) {
+            ptx::tma_load_2d(b_dst, tmB, full_bar(s), kb * BKE, ti.n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / NPB; ++j) {
+              ptx::tma_load_2d(b_dst + j * (BKE * ROW_BYTES), tmB, full_bar(s), ti.n0 + j * NPB, kb * BKE);
+            }
+          }
+        }
+      }
+      // Drain: every load this thread armed has either landed or is given a bounded time to.
+      const uint32_t last = it;
+      const uint32_t first = last > (uint32_t)STAGES ? last - STAGES : 0u;
+      for (uint32_t i = first; i < last; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1u;
+        uint32_t spins = 0;
+        while (!ptx::mbar_try_wait(full_bar(s), ph) && ++spins < (1u << 16)) {
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ============================================================ MMA issuer
+    if (lane == 0) {
+      // Shared-memory matrix descriptor: version 1 (bit 46), 128-byte swizzle (2 << 61),
+      // stride byte offset 1024 (8 rows x 128 B) in 16-byte units at bit 32.
+      const uint64_t desc_common = (uint64_t(1) << 46) | (uint64_t(2) << 61) | (uint64_t(1024 >> 4) << 32);
+      const uint64_t desc_kmajor = desc_common | (uint64_t(1) << 16);
+      const uint64_t desc_nmajor = desc_common | (uint64_t((BKE * ROW_BYTES) >> 4) << 16);
+      // Instruction descriptor: fp32 accumulate, A/B format (bf16 = 1, e4m3 = 0), M = 128.
+      const uint32_t fmt = FP8 ? 0u : 1u;
+      const uint32_t idesc_base = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(BM >> 4) << 24);
+      uint32_t it = 0;
+      uint32_t lt = 0;  // local tile counter
+      bool ok = true;
+      for (int t = blockIdx.x; t < sched.total_tiles && ok; t += gridDim.x, ++lt) {
+        const TileInfo ti = decode_tile<BN>(p, sched, t);
+        const uint32_t acc = lt & 1u;
+        const uint32_t aph = (lt >> 1) & 1u;
+        ok = mbar_wait(tempty_bar(acc), aph ^ 1u, p, abort_flag);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        const bool nmajor = p.b_nmajor[ti.b] != 0;
+        const int n_eff = min(BN, (ti.n_valid + 15) & ~15);
+        const uint32_t idesc = idesc_base | (nmajor ? (1u << 16) : 0u) | (uint32_t(n_eff >> 3) << 17);
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint64_t bdesc_hi = nmajor ? desc_nmajor : desc_kmajor;
+        const uint32_t bstep = nmajor ? uint32_t((UMMA_K * ROW_BYTES) >> 4) : 2u;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          ok = mbar_wait(full_bar(s), ph, p, abort_flag);
+          if (!ok) break;
+          ptx::tc_fence_after();
+          const uint32_t a_addr = smem_base + s * L::STAGE_BYTES;
+          const uint32_t b_addr = a_addr + L::A_BYTES;
+          const uint64_t adesc = desc_kmajor | uint64_t((a_addr >> 4) & 0x3fffu);
+          const uint64_t bdesc = bdesc_hi | uint64_t((b_addr >> 4) & 0x3fffu);
+#pragma unroll
+          for (int k = 0; k < KSTEPS; ++k) {
+            const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+            if (FP8) {
+              ptx::mma_f8(d_tmem, adesc + 2u * k, bdesc + bstep * k, idesc, accum);
+            } else {
+              ptx::mma_f16(d_tmem, adesc + 2u * k, bdesc + bstep * k, idesc, accum);
+            }
+          }
+          ptx::tc_commit(empty_bar(s));
+        }
+        if (ok) ptx::tc_commit(tfull_bar(acc));
+      }
+      // Make sure nothing this thread issued is still running before TMEM is freed.
+      ptx::tc_commit(drain_bar);
+      uint32_t spins = 0;
+      while (!ptx::mbar_try_wait(drain_bar, 0) && ++spins < (1u << 20)) {
+      }
+    }
+    __syncwarp();
+  } else if (warp < 2 + EPI_WARPS) {
+    // ============================================================ epilogue
+    const int quarter = warp & 3;                   // TMEM lanes this warp may read
+    const int row_in_tile = quarter * 32 + lane;
+    const bool epi_leader = (warp == 2 && lane == 0);
+    uint32_t lt = 0;
+    for (int t = blockIdx.x; t < sched.total_tiles; t += gridDim.x, ++lt) {
+      const TileInfo ti = decode_tile<BN>(p, sched, t);
+      const uint32_t acc = lt & 1u;
+      const uint32_t aph = (lt >> 1) & 1u;
+      const bool row_ok = row_in_tile < ti.rows_valid;
+      const int chunk_row = ti.mt * BM + row_in_tile;                   // row inside the chunk
+      const long long grow = (long long)ti.chunk * p.rows_per_rank + chunk_row;  // row of the full matrix
+      const int b = ti.b;
+      const bool own = (p.mode != MODE_RS) || (ti.chunk == p.rank);
+
+      // Row / tile constants of the scaled epilogue.
+      float sa = 1.0f;
+      if (p.a_scale_mode == 1) {
+        sa = __ldg(p.a_scale_full);
+      } else if (p.a_scale_mode == 2 && row_ok) {
+        if (p.mode == MODE_AG && p.a_scale_own != nullptr) {
+          sa = (ti.chunk == p.rank) ? __ldg(p.a_scale_own + chunk_row) : __ldcg(p.ag_scale_gathered + grow);
+        } else {
+          sa = __ldg(p.a_scale_full + grow);
+        }
+      }
+      const float* bs = p.b_scale[b];
+      const int bs_mode = p.b_scale_mode[b];
+      if (bs_mode == 1) sa *= __ldg(bs);
+      const float rscale = (p.result_scale[b] != nullptr) ? __ldg(p.result_scale[b]) : 1.0f;
+      const void* bias = p.bias[b];
+      const bool scaled = (p.a_scale_mode != 0) || (bs_mode != 0) || (bias != nullptr) || (p.result_scale[b] != nullptr);
+
+      // One thread does the waiting (peers' partials for a tile this rank owns, then the
+      // accumulator); its verdict is shared so that all four warps leave the loop together.
+      if (epi_leader) {
+        bool good = true;
+        if (p.mode == MODE_RS && own && p.ws > 1) {
+          for (int src = 0; src < p.ws && good; ++src) {
+            if (src == p.rank) continue;
+            good = flag_wait<true>(p.rs_flag_local + (size_t)src * p.rs_max_tiles + ti.tile_in_chunk, p.epoch, p,
+                                   abort_flag, ST_TIMEOUT_PARTIAL, (uint32_t)src);
+          }
+        }
+        if (good) good = mbar_wait(tfull_bar(acc), aph, p, abort_flag);
+        epi_verdict[lt & 1u] = good ? 1u : 0u;
+      }
+      ptx::named_bar_sync(1, EPI_WARPS * 32);
+      if (epi_verdict[lt & 1u] == 0u) break;
+      ptx::tc_fence_after();
+
+      const bool o32 = p.out_fp32[b] != 0;
+      const int oes = o32 ? 4 : 2;
+      const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        if (c * 32 >= ti.n_valid) break;   // uniform across the warp
+        uint32_t raw[32];
+        ptx::tmem_ld_32x32(t_row + c * 32, raw);
+        ptx::tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+        const int col0 = ti.n0 + c * 32;
+        const int nvalid = min(32, p.N[b] - col0);
+        if (scaled) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float x = v[j] * sa;
+            if (j < nvalid) {
+              if (bs_mode == 2) x *= __ldg(bs + col0 + j);
+              if (bias != nullptr) {
+                x += p.bias_fp32[b] ? __ldg(reinterpret_cast<const float*>(bias) + col0 + j)
+                                    : __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(bias) + col0 + j));
+              }
+            }
+            v[j] = x * rscale;
+          }
+        }
+        if (row_ok) {
+          if (p.mode != MODE_RS) {
+            uint8_t* dst = reinterpret_cast<uint8_t*>(p.out[b]) + ((size_t)grow * p.ldo[b] + col0) * oes;
+            store_row32(dst, v, nvalid, o32);
+          } else if (!own) {
+            // Partial for another rank: straight into its arena, slot = this rank.
+            uint8_t* dst = p.rs_arena_peer[ti.chunk] +
+                           (((size_t)p.rank * p.rows_per_rank + chunk_row) * p.N[b] + col0) * oes;
+            store_row32(dst, v, nvalid, o32);
+          } else {
+            for (int src = 0; src < p.ws; ++src) {
+              if (src == p.rank) continue;
+              const uint8_t* part = p.rs_arena_local +
+                                    (((size_t)src * p.rows_per_rank + chunk_row) * p.N[b] + col0) * oes;
+              add_row32(part, v, nvalid, o32);
+            }
+            if (p.reduce_scale != 1.0f) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] *= p.reduce_scale;
+            }
+            uint8_t* dst = reinterpret_cast<uint8_t*>(p.out[b]) + ((size_t)chunk_row * p.ldo[b] + col0) * oes;
+            store_row32(dst, v, nvalid, o32);
+          }
+        }
+      }
+      // Release the accumulator to the MMA warp.
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+
+      if (p.mode == MODE_RS && !own) {
+        // Publish the tile to its owner: all 128 threads' stores, then one system-scope release.
+        __threadfence_system();
+        ptx::named_bar_sync(2, EPI_WARPS * 32);
+        if (epi_leader) {
+          ptx::st_release_sys(p.rs_flag_peer[ti.chunk] + (size_t)p.rank * p.rs_max_tiles + ti.tile_in_chunk, p.epoch);
+        }
+      }
+    }
+  } else {
+    // ============================================================ communication warps (all-gather)
+    if (p.mode == MODE_AG) {
+      const int cw = warp - (2 + EPI_WARPS);
+      const int gw = blockIdx.x * COMM_WARPS + cw;
+      const int total_warps = gridDim.x * COMM_WARPS;
+      const int full_pieces = ag_tile_pieces(p, 0);
+      const int total_pieces = (int)((p.ag_chunk_bytes + PIECE_BYTES - 1) / PIECE_BYTES);  // flat, staging only
+      // ---- step 0: stage the local shard for the peers (and in the gathered buffer if asked).
+      const bool stage_symm = p.ws > 1;
+      if (stage_symm || p.ag_copy_own) {
+        uint8_t* dst_a = stage_symm ? p.ag_symm_local : p.ag_gathered + (size_t)p.rank * p.ag_chunk_bytes;
+        uint8_t* dst_b = (stage_symm && p.ag_copy_own) ? p.ag_gathered + (size_t)p.rank * p.ag_chunk_bytes : nullptr;
+        for (int q = gw; q < total_pieces; q += total_warps) {
+          const long long off = (long long)q * PIECE_BYTES;
+          const int n16 = (int)(min((long long)PIECE_BYTES, p.ag_chunk_bytes - off) >> 4);
+          copy_piece<false>(p.ag_src + off, dst_a + off, dst_b ? dst_b + off : nullptr, n16, lane);
+        }
+        if (p.ag_has_scale && stage_symm) {
+          float* sdst = reinterpret_cast<float*>(p.ag_symm_local + p.ag_scale_off);
+          for (int i = gw * 32 + lane; i < p.rows_per_rank; i += total_warps * 32) sdst[i] = __ldg(p.ag_scale_src + i);
+        }
+      }
+      if (stage_symm) {
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const uint32_t prev = atomicAdd(p.ctrl, 1u);
+          if (prev == (uint32_t)total_warps - 1u) {
+            __threadfence_system();
+            for (int r = 0; r < p.ws; ++r) {
+              if (r != p.rank) ptx::st_release_sys(p.staged_peer[r] + p.rank * FLAG_STRIDE, p.epoch);
+            }
+          }
+        }
+        __syncwarp();
+      }
+      // ---- steps 1..ws-1: pull rank+step's shard, row block by row block.
+      bool ok = true;
+      for (int step = 1; step < p.ws && ok; ++step) {
+        const int src = (p.rank + step) % p.ws;
+        if (lane == 0) {
+          ok = flag_wait<true>(p.staged_local + src * FLAG_STRIDE, p.epoch, p, abort_flag, ST_TIMEOUT_STAGED, (uint32_t)src);
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+        const uint8_t* peer = p.ag_symm_peer[src];
+        uint8_t* dst = p.ag_gathered + (size_t)src * p.ag_chunk_bytes;
+        const long long tile_bytes = (long long)BM * p.K * p.elem_bytes;
+        const int chunk_pieces = (sched.mt_per_chunk - 1) * full_pieces + ag_tile_pieces(p, sched.mt_per_chunk - 1);
+        uint32_t* ready = p.ready + src * sched.mt_per_chunk;
+        if (p.ag_has_scale) {
+          const float* ps = reinterpret_cast<const float*>(peer + p.ag_scale_off);
+          float* gs = p.ag_scale_gathered + (size_t)src * p.rows_per_rank;
+          for (int mt = gw; mt < sched.mt_per_chunk; mt += total_warps) {
+            const int rows = min(BM, p.rows_per_rank - mt * BM);
+            for (int i = lane; i < rows; i += 32) {
+              uint32_t w;
+              asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(w) : "l"(ps + mt * BM + i) : "memory");
+              gs[mt * BM + i] = __uint_as_float(w);
+            }
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) ptx::red_add_release_gpu(ready + mt, 1u);
+          }
+        }
+        for (int q = gw; q < chunk_pieces; q += total_warps) {
+          const int mt = q / full_pieces;
+          const int j = q - mt * full_pieces;
+          const long long tile_start = (long long)mt * tile_bytes;
+          const long long tile_end = min(tile_start + tile_bytes, (long long)p.ag_chunk_bytes);
+          const long long off = tile_start + (long long)j * PIECE_BYTES;
+          const int n16 = (int)(min((long long)PIECE_BYTES, tile_end - off) >> 4);
+          copy_piece<true>(peer + off, dst + off, nullptr, n16, lane);
+          ptx::fence_proxy_async_global();
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) ptx::red_add_release_gpu(ready + mt, 1u);
+        }
+      }
+    }
+  }
+
+  // ============================================================ teardown
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace apk

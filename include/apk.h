@@ -1,0 +1,169 @@
+/*
+ * apk.h - C ABI of libapk.so, the sm_100a (B200) implementation of AutoParallel's async
+ * tensor-parallel hot path: all-gather -> matmul and matmul -> reduce-scatter, bf16 and fp8
+ * (e4m3, row-wise scales), with the communication done inside the GEMM kernel over NVLink
+ * peer mappings.
+ *
+ * The library takes plain device pointers, sizes and a CUDA stream handle; it knows nothing
+ * about torch. Every function returns 0 on success or a negative code; apk_last_error()
+ * gives the message of the calling thread's last failure. Nothing here falls back to the
+ * CPU: on a machine without an sm_100 GPU the op entry points fail with APK_ERR_CUDA.
+ *
+ * Reference interfaces replaced (paths inside the AutoParallel source tree):
+ *   apk_ag_gemm            autoparallel/asynctp_ops.py:395-530  _fused_all_gather_matmul_impl
+ *                          + :34-177 _pipelined_multi_all_gather_and_consume, as called by
+ *                          the CUDA bodies of fused_all_gather_matmul (:703-752) and
+ *                          fused_all_gather_scaled_matmul (:947-1025)
+ *   apk_gemm_rs            autoparallel/asynctp_ops.py:1103-1185 _fused_matmul_reduce_scatter_impl,
+ *                          :1293-1423 _fused_scaled_matmul_reduce_scatter_impl and
+ *                          :209-323 _pipelined_produce_and_all2all
+ *   apk_symm_*             the parts of torch's symmetric memory the path uses through
+ *                          get_symm_mem_workspace / get_buffer / barrier
+ *                          (autoparallel/asynctp_ops.py:61-65, :89-94, :229-242)
+ */
+#ifndef APK_H_
+#define APK_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define APK_ABI_VERSION 1
+#define APK_MAX_B 4      /* weight matrices that may share one gathered A */
+#define APK_MAX_WORLD 8  /* ranks of one tensor-parallel group (one NVSwitch domain) */
+
+enum {
+  APK_OK = 0,
+  APK_ERR_ARG = -1,     /* bad argument (shape, alignment, dtype, null pointer) */
+  APK_ERR_CUDA = -2,    /* a CUDA runtime or driver call failed */
+  APK_ERR_SIZE = -3,    /* a workspace, flag pad or fixed scratch area is too small */
+  APK_ERR_TIMEOUT = -4, /* a device-side wait ran out (reported by apk_check_status) */
+};
+
+enum { APK_BF16 = 0, APK_E4M3 = 1, APK_F32 = 2 };
+
+/* How a scale operand is laid out. */
+enum {
+  APK_SCALE_NONE = 0,
+  APK_SCALE_SCALAR = 1,        /* one fp32 */
+  APK_SCALE_VECTOR = 2,        /* A: one fp32 per row of the local operand; B: one per column */
+  APK_SCALE_ROWS_REPLICATED = 3 /* A of an all-gather: one fp32 per row of the gathered A */
+};
+
+enum { APK_REDUCE_SUM = 0, APK_REDUCE_AVG = 1 };
+
+/*
+ * One tensor-parallel group as seen from this process. data[r] / flags[r] are rank r's
+ * symmetric data arena and signal pad mapped into this process (entry [rank] is the local
+ * allocation); they come from apk_symm_alloc / apk_symm_import and have the same size on
+ * every rank. The data arena is used in two halves that alternate with the parity of
+ * `epoch`, which the caller increments by one for every collective call on the group (all
+ * ranks call in the same order, so they agree on it). With world == 1, data and flags may
+ * be null.
+ *
+ * Replaces what the reference gets from get_symm_mem_workspace(group_name, size)
+ * (autoparallel/asynctp_ops.py:61, :229) plus symm_mem.barrier(channel) (:65, :147, :177,
+ * :233, :311-323): there are no separate barrier kernels, the fused kernel releases and
+ * acquires per-chunk flags itself.
+ */
+typedef struct {
+  int32_t rank;
+  int32_t world;
+  void* data[APK_MAX_WORLD];
+  void* flags[APK_MAX_WORLD];
+  uint64_t data_bytes;  /* size of each data arena (both halves together) */
+  uint64_t flag_bytes;  /* size of each signal pad, at least 4096 */
+  void* ctrl;           /* local device scratch for per-call counters */
+  uint64_t ctrl_bytes;
+  uint32_t* status;     /* local device word; 0 while no device wait has timed out */
+  uint32_t epoch;
+  uint32_t reserved;
+  double timeout_s;     /* budget of every device-side wait */
+} apk_comm;
+
+/* One right-hand operand and its output. B is [K, N]. */
+typedef struct {
+  const void* B;
+  int64_t ldb;           /* elements between rows (n_major) or between columns (k-contiguous) */
+  int32_t n_major;       /* 1: row-major [K][N]; 0: column-major, K contiguous (B = W^T view) */
+  int32_t N;
+  void* out;             /* AG: [world*rows_per_rank, N]; RS: [M/world, N] */
+  int64_t ldo;
+  int32_t out_dtype;     /* APK_BF16 or APK_F32 */
+  int32_t b_scale_mode;  /* APK_SCALE_NONE / SCALAR / VECTOR (per column) */
+  const float* b_scale;
+  const void* bias;      /* per column, or null */
+  int32_t bias_dtype;    /* APK_BF16 or APK_F32 */
+  int32_t reserved;
+  const float* result_scale; /* one fp32 or null */
+} apk_operand;
+
+/*
+ * outs[b] = all_gather(A_shard) @ Bs[b], rows ordered by source rank.
+ * Mirrors _fused_all_gather_matmul_impl (autoparallel/asynctp_ops.py:395-530) after it has
+ * moved gather_dim to the front and flattened A to 2-D (:437-443).
+ */
+typedef struct {
+  int32_t dtype;          /* APK_BF16 or APK_E4M3: element type of A and every B */
+  int32_t rows_per_rank;  /* rows of A_shard */
+  int32_t K;
+  int32_t nB;
+  const void* A_shard;    /* [rows_per_rank, K], row-major with lda */
+  int64_t lda;
+  apk_operand Bs[APK_MAX_B];
+  void* A_gathered;       /* [world*rows_per_rank, K] contiguous. Required when world > 1 or return_A. */
+  int32_t return_A;       /* also place the local shard in A_gathered */
+  int32_t a_scale_mode;   /* NONE / SCALAR / VECTOR (row-wise, sharded like A) / ROWS_REPLICATED */
+  const float* A_scale;
+  float* A_scale_gathered; /* [world*rows_per_rank] scratch, required for VECTOR when world > 1 */
+} apk_ag_gemm_args;
+
+/*
+ * out = reduce_scatter(A @ B) along rows: rank d receives rows [d*M/world, (d+1)*M/world)
+ * summed (or averaged) over ranks. Mirrors _fused_matmul_reduce_scatter_impl
+ * (autoparallel/asynctp_ops.py:1159-1185) after scatter_dim was moved to the front.
+ */
+typedef struct {
+  int32_t dtype;
+  int32_t M;              /* rows of A; divisible by world */
+  int32_t K;
+  int32_t reduce_op;      /* APK_REDUCE_SUM / APK_REDUCE_AVG */
+  const void* A;          /* [M, K] row-major with lda */
+  int64_t lda;
+  apk_operand B;          /* B.out is [M/world, N] */
+  int32_t a_scale_mode;   /* NONE / SCALAR / VECTOR (one per row of A) */
+  int32_t reserved;
+  const float* A_scale;
+} apk_gemm_rs_args;
+
+int apk_abi_version(void);
+const char* apk_last_error(void);
+
+/* ---- symmetric memory: cudaMalloc + CUDA IPC handles (one process per GPU). ---- */
+int apk_symm_alloc(uint64_t bytes, void** ptr);             /* zero-filled, on the current device */
+int apk_symm_free(void* ptr);
+int apk_symm_export(const void* ptr, uint8_t handle[64]);   /* handle to ship to the peers */
+int apk_symm_import(const uint8_t handle[64], void** ptr);  /* map a peer's allocation */
+int apk_symm_unimport(void* ptr);
+
+/* Bytes the ops need in each HALF of the data arena / in ctrl / tiles of the flag pad. */
+uint64_t apk_ag_gemm_arena_bytes(const apk_ag_gemm_args* args, int32_t world);
+uint64_t apk_gemm_rs_arena_bytes(const apk_gemm_rs_args* args, int32_t world);
+uint64_t apk_ctrl_bytes(int32_t rows_per_rank, int32_t world);
+
+/* ---- ops: enqueue on `stream` (a cudaStream_t) of the current device and return. ---- */
+int apk_ag_gemm(const apk_comm* comm, const apk_ag_gemm_args* args, void* stream);
+int apk_gemm_rs(const apk_comm* comm, const apk_gemm_rs_args* args, void* stream);
+
+/* Synchronises `stream`, reads the status word, clears it; APK_ERR_TIMEOUT if it was set. */
+int apk_check_status(const apk_comm* comm, void* stream, uint32_t* raw);
+
+/* Kernels launched by this library in this process so far (memsets not counted). */
+uint64_t apk_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* APK_H_ */
