@@ -1,0 +1,193 @@
+"""Symmetric buffers and signal pads, one set per process-group name.
+
+Replaces what the reference obtains from ``get_symm_mem_workspace(group_name, min_size)`` and
+``symm_mem.barrier(channel)`` (autoparallel/asynctp_ops.py:61-65, :229-242): a grow-only data
+arena that every rank of the group can address on every peer, plus a zero-initialised signal
+pad. Memory comes from ``apk_symm_alloc`` (cudaMalloc) and is mapped into the peers with CUDA
+IPC handles exchanged through the process group, one process per GPU.
+
+Protocol facts the kernels rely on (kept here because this module owns ``epoch``):
+
+* every collective op on a group increments ``epoch`` by one on every rank (all ranks call in
+  the same order, like any collective);
+* the data arena is used in two halves selected by ``epoch & 1``; in every op each rank waits
+  for a signal that every other rank produces during the same op, so a rank that has reached
+  op ``e + 2`` knows that all peers have finished op ``e`` and may overwrite that half;
+* flags carry epoch values and are compared with ``>=``, so they are never reset.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+import torch.distributed.distributed_c10d as c10d
+
+from . import _native as nat
+
+FLAG_PAD_BYTES = 4096 + 4 * nat.APK_MAX_WORLD * 65536  # staged flags + 65536 tile flags per source rank
+DEFAULT_TIMEOUT_S = 30.0
+
+
+def _round_up(x: int, a: int) -> int:
+    return (x + a - 1) // a * a
+
+
+@dataclass
+class PeerHandles:
+    """Peer-mapped addresses of one group: index = rank inside the group."""
+
+    rank: int
+    world: int
+    data: list[int] = field(default_factory=list)
+    flags: list[int] = field(default_factory=list)
+    data_bytes: int = 0
+    flag_bytes: int = 0
+
+
+class GroupWorkspace:
+    """Arena + signal pad + per-call scratch of one process group on this rank."""
+
+    def __init__(self, group_name: str, device: torch.device):
+        self.group_name = group_name
+        self.group = c10d._resolve_process_group(group_name)
+        self.rank = dist.get_rank(self.group)
+        self.world = self.group.size()
+        if self.world > nat.APK_MAX_WORLD:
+            raise ValueError(f"group {group_name!r} has {self.world} ranks; at most {nat.APK_MAX_WORLD} are supported")
+        self.device = device
+        self.epoch = 0
+        self.timeout_s = DEFAULT_TIMEOUT_S
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.ctrl = torch.zeros(1024, dtype=torch.int32, device=device)
+        self.handles = PeerHandles(self.rank, self.world)
+        self._local_data = 0
+        self._local_flags = 0
+        self._imported: list[int] = []
+
+    # ------------------------------------------------------------------ allocation
+    def _exchange(self, ptr: int) -> list[int]:
+        """All ranks publish the IPC handle of ``ptr``; returns the peer-mapped addresses."""
+        L = nat.lib()
+        buf = C.create_string_buffer(64)
+        nat.check(L.apk_symm_export(C.c_void_p(ptr), buf))
+        gathered: list[bytes | None] = [None] * self.world
+        dist.all_gather_object(gathered, buf.raw, group=self.group)
+        out = []
+        for r, h in enumerate(gathered):
+            if r == self.rank:
+                out.append(ptr)
+                continue
+            p = C.c_void_p()
+            nat.check(L.apk_symm_import(C.create_string_buffer(h, 64), C.byref(p)))
+            self._imported.append(p.value)
+            out.append(p.value)
+        return out
+
+    def _release(self) -> None:
+        L = nat.lib()
+        for p in self._imported:
+            L.apk_symm_unimport(C.c_void_p(p))
+        self._imported = []
+        if self._local_data:
+            L.apk_symm_free(C.c_void_p(self._local_data))
+            self._local_data = 0
+        if self._local_flags:
+            L.apk_symm_free(C.c_void_p(self._local_flags))
+            self._local_flags = 0
+
+    def ensure(self, half_bytes: int, ctrl_bytes: int) -> None:
+        """Grow the arena so that each half holds ``half_bytes``. Collective when it grows:
+        shapes are congruent across ranks, so every rank takes the same decision."""
+        if ctrl_bytes > self.ctrl.numel() * 4:
+            self.ctrl = torch.zeros(_round_up(ctrl_bytes, 4096) // 4, dtype=torch.int32, device=self.device)
+        if self.world == 1:
+            return
+        need = 2 * _round_up(half_bytes, 4096)
+        if need <= self.handles.data_bytes and self._local_flags:
+            return
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("the symmetric workspace cannot grow during CUDA graph capture")
+        L = nat.lib()
+        # Nobody may still be reading the old arena: drain the device, then meet the peers.
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        self._release()
+        need = max(need, 2 * self.handles.data_bytes)
+        with torch.cuda.device(self.device):
+            p = C.c_void_p()
+            nat.check(L.apk_symm_alloc(need, C.byref(p)))
+            self._local_data = p.value
+            f = C.c_void_p()
+            nat.check(L.apk_symm_alloc(FLAG_PAD_BYTES, C.byref(f)))
+            self._local_flags = f.value
+            self.handles.data = self._exchange(self._local_data)
+            self.handles.flags = self._exchange(self._local_flags)
+        self.handles.data_bytes = need
+        self.handles.flag_bytes = FLAG_PAD_BYTES
+        dist.barrier(group=self.group)
+
+    # ------------------------------------------------------------------ per call
+    def next_comm(self) -> nat.ApkComm:
+        """The comm descriptor of the next collective op (advances the epoch)."""
+        self.epoch = (self.epoch + 1) & 0xFFFFFFFF
+        c = nat.ApkComm()
+        c.rank = self.rank
+        c.world = self.world
+        for r in range(self.world if self.handles.data else 0):
+            c.data[r] = self.handles.data[r]
+            c.flags[r] = self.handles.flags[r]
+        c.data_bytes = self.handles.data_bytes
+        c.flag_bytes = self.handles.flag_bytes
+        c.ctrl = self.ctrl.data_ptr()
+        c.ctrl_bytes = self.ctrl.numel() * 4
+        c.status = self.status.data_ptr()
+        c.epoch = self.epoch
+        c.timeout_s = self.timeout_s
+        return c
+
+    def check_status(self) -> None:
+        """Synchronise and raise if a device-side wait timed out since the last check."""
+        c = self.next_comm()
+        self.epoch = (self.epoch - 1) & 0xFFFFFFFF  # not a collective: give the epoch back
+        raw = C.c_uint32(0)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        nat.check(nat.lib().apk_check_status(C.byref(c), C.c_void_p(stream), C.byref(raw)))
+
+    def close(self) -> None:
+        self._release()
+        self.handles = PeerHandles(self.rank, self.world)
+
+
+_workspaces: dict[str, GroupWorkspace] = {}
+
+
+def get_workspace(group_name: str, device: torch.device) -> GroupWorkspace:
+    """Workspace of ``group_name`` on this rank (created on first use)."""
+    ws = _workspaces.get(group_name)
+    if ws is None:
+        ws = GroupWorkspace(group_name, device)
+        _workspaces[group_name] = ws
+    return ws
+
+
+def peer_handles(group_name: str) -> PeerHandles:
+    """The group_name -> NVLink peer-handle map: addresses of every rank's arena and pad."""
+    if group_name not in _workspaces:
+        raise KeyError(f"no symmetric workspace has been created for group {group_name!r}")
+    return _workspaces[group_name].handles
+
+
+def sync_check(group_name: str | None = None) -> None:
+    """Raise ``ApkError`` if any fused op on the group(s) hit a device-side timeout."""
+    for name, ws in _workspaces.items():
+        if group_name is None or name == group_name:
+            ws.check_status()
+
+
+def shutdown() -> None:
+    """Free every workspace (call before destroying the process group)."""
+    for ws in _workspaces.values():
+        ws.close()
+    _workspaces.clear()
