@@ -82,7 +82,7 @@ def _check_and_verify_fp8_all_gather_scale_mode(
         return _ScaleMode.UNSCALED
     gathered_shape = list(shard.shape)
     gathered_shape[gather_dim] *= group_size
-    if scale.shape[-1] == 1 and scale.shape[:-1] == shard.shape[:-1]:
+    if scale.shape[:-1] == shard.shape[:-1] and scale.shape[-1] == 1:
         return _ScaleMode.ROW_WISE_SHARDED
     if scale.numel() == 1:
         return _ScaleMode.TENSOR_WISE

@@ -1,0 +1,346 @@
+"""Benchmark of the async-TP hot path on B200: fused all-gather->matmul + matmul->reduce-scatter.
+
+    python bench.py --gpus N --steps K --warmup W            # this repository's kernels
+    python bench.py --impl reference --gpus N ...            # the reference's unfused CPU path
+
+Workload (BASELINE config 2, Llama-3-8B MLP at TP 8, bf16): 32768 tokens x hidden 4096 sharded
+along the sequence over the N ranks; every rank holds the TP-8 weight slices w1, w3 [4096,1792]
+and w2 [1792,4096] whatever N is, so the work per GPU is fixed (weak scaling). One step =
+fused_all_gather_matmul(x_shard, [w1, w3]) followed by fused_matmul_reduce_scatter(h, w2) with
+h = silu(h1) * h3 [32768,1792]. Synthetic data: activations ~N(0,1) seeded by rank, weights
+~N(0,0.02). Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+TOKENS, HIDDEN, FFN_PER_RANK = 32768, 4096, 1792
+FLOPS_AG = FLOPS_RS = FLOPS_STEP = 0.0
+
+
+def _set_tokens(tokens: int) -> None:
+    """--tokens shrinks the workload (ncu captures); the default is the BASELINE size."""
+    global TOKENS, FLOPS_AG, FLOPS_RS, FLOPS_STEP
+    TOKENS = tokens
+    FLOPS_AG = 2.0 * TOKENS * HIDDEN * (2 * FFN_PER_RANK)   # per GPU, w1 and w3
+    FLOPS_RS = 2.0 * TOKENS * FFN_PER_RANK * HIDDEN         # per GPU, w2
+    FLOPS_STEP = FLOPS_AG + FLOPS_RS
+
+
+_set_tokens(TOKENS)
+NOMINAL_BF16 = 2.25e15      # dense bf16 peak named by the task
+NVLINK_BPS = 900e9          # per direction per GPU, nominal
+METRIC = "AG+GEMM / GEMM+RS TFLOP/s (whole job; per-GPU and % of roofline beside it)"
+CPU_SAMPLE_TOKENS = 4096    # the CPU arms run this many of the 32768 tokens per step
+
+
+def _peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d.get("bf16_tflops_sustained") or d.get("bf16_tflops"), "measured"
+    return 1400.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.path = index, None, None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                stdout=f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in Path(self.path).read_text().splitlines():
+            c = [x.strip() for x in line.split(",")]
+            if len(c) < 9:
+                continue
+            try:
+                sm.append(float(c[1])); mx.append(float(c[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, c[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------ CPU arms
+def _cpu_worker(rank, world, initfile, steps, warmup, threads, out_path, tokens):
+    import torch
+    import torch.distributed as dist
+
+    from oracle import asynctp_oracle as orc
+
+    _set_tokens(tokens)
+    torch.set_num_threads(threads)
+    dist.init_process_group("gloo", init_method=f"file://{initfile}", rank=rank, world_size=world)
+    rows = CPU_SAMPLE_TOKENS // world
+    x = orc.activations(rank, rows, HIDDEN, torch.float32)
+    w1, w3 = orc.weights(7, HIDDEN, FFN_PER_RANK, torch.float32), orc.weights(8, HIDDEN, FFN_PER_RANK, torch.float32)
+    w2 = orc.weights(9, FFN_PER_RANK, HIDDEN, torch.float32)
+    h = orc.activations(50 + rank, CPU_SAMPLE_TOKENS, FFN_PER_RANK, torch.float32)
+
+    def step():
+        orc.all_gather_matmul_dist(x, [w1, w3], 0, return_A=False)
+        orc.matmul_reduce_scatter_dist(h, w2, "sum", 0)
+
+    for _ in range(warmup):
+        step()
+    dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dist.barrier()
+    dt = time.perf_counter() - t0
+    if rank == 0:
+        Path(out_path).write_text(json.dumps({"seconds": dt}))
+    dist.destroy_process_group()
+
+
+def cpu_unfused(world: int, steps: int, warmup: int) -> dict:
+    """The reference's unfused decomposition (oracle port of autoparallel/asynctp_ops.py:672-700,
+    :1090-1100) on `world` gloo ranks sharing the host cores, on CPU_SAMPLE_TOKENS of the tokens."""
+    import torch.multiprocessing as mp
+
+    cores = os.cpu_count() or 1
+    threads = max(1, cores // world)
+    with tempfile.TemporaryDirectory() as d:
+        out = os.path.join(d, "out.json")
+        mp.spawn(_cpu_worker, args=(world, os.path.join(d, "init"), steps, warmup, threads, out, TOKENS), nprocs=world, join=True)
+        dt = json.loads(Path(out).read_text())["seconds"]
+    frac = CPU_SAMPLE_TOKENS / TOKENS
+    ms = dt / steps * 1e3
+    tflops = world * FLOPS_STEP * frac / (ms * 1e-3) / 1e12
+    return {"value": tflops, "unit": "TFLOP/s", "cores": threads * world, "kind": "port", "ms_per_step": ms,
+            "sample": f"{CPU_SAMPLE_TOKENS} of {TOKENS} tokens per step, fp32, {world} gloo rank(s) x {threads} threads, "
+                      f"{steps} steps after {warmup} warm-up"}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n = args.gpus
+    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    base = cpu_unfused(n, steps, warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "TFLOP/s", "n_gpus": n,
+        "steps": steps, "warmup": warmup, "ms_per_step": base["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": _config(n, "cpu"),
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def _config(n: int, where: str) -> dict:
+    return {
+        "workload": "llama3_8b_mlp_tp8_slices (BASELINE config 2)", "tokens": TOKENS, "hidden": HIDDEN,
+        "ffn_per_rank": FFN_PER_RANK, "tp": n, "rows_per_rank": TOKENS // n,
+        "ops": "fused_all_gather_matmul(x,[w1,w3]) + fused_matmul_reduce_scatter(h,w2)",
+        "l2": "working set per step (x 268MB/tp, weights 44MB, h1/h3 235MB, h 117MB) exceeds the 126MB L2" if where == "gpu" else "n/a",
+    }
+
+
+# ------------------------------------------------------------------------------------------ GPU arm
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    else:
+        with tempfile.TemporaryDirectory() as d:
+            dist.init_process_group("gloo", init_method=f"file://{os.path.join(d, 'init')}", rank=0, world_size=1)
+
+    from autoparallel_b200 import _native as nat
+    from autoparallel_b200 import symm
+    from autoparallel_b200.build import build_native
+    import autoparallel_b200.asynctp_ops  # noqa: F401
+    from oracle import asynctp_oracle as orc  # input generators only; nothing computes through it here
+
+    build_native()
+    L = nat.lib()
+    ns = torch.ops._ap_symm_mem
+    g = dist.group.WORLD.group_name
+    rows = TOKENS // world
+    K, W = args.steps, args.warmup
+
+    x_host = orc.activations(rank, rows, HIDDEN).pin_memory()
+    x = x_host.to(dev)
+    w1, w3 = orc.weights(7, HIDDEN, FFN_PER_RANK).to(dev), orc.weights(8, HIDDEN, FFN_PER_RANK).to(dev)
+    w2 = orc.weights(9, FFN_PER_RANK, HIDDEN).to(dev)
+    _, (h1, h3) = ns.fused_all_gather_matmul(x, [w1, w3], 0, g, return_A=False)
+    h = torch.nn.functional.silu(h1.float()).mul_(h3.float()).to(torch.bfloat16)
+    del h1, h3
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    def step():
+        ns.fused_all_gather_matmul(x, [w1, w3], 0, g, return_A=False)
+        ns.fused_matmul_reduce_scatter(h, w2, "sum", 0, g)
+
+    for _ in range(max(W, 3)):
+        step()
+    sync_all()
+
+    # ---- timed region: K steps, device-resident inputs; per-op events ride along on the same stream
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = L.apk_launch_count()
+    sync_all()
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin.record()
+    for i in range(K):
+        ev[i][0].record()
+        ns.fused_all_gather_matmul(x, [w1, w3], 0, g, return_A=False)
+        ev[i][1].record()
+        ns.fused_matmul_reduce_scatter(h, w2, "sum", 0, g)
+        ev[i][2].record()
+    t_end.record()
+    sync_all()
+    launches = L.apk_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = max_over_ranks(t_begin.elapsed_time(t_end) / K)
+    ms_ag = max_over_ranks(statistics.mean(e[0].elapsed_time(e[1]) for e in ev))
+    ms_rs = max_over_ranks(statistics.mean(e[1].elapsed_time(e[2]) for e in ev))
+    symm.sync_check()
+
+    # ---- end to end: host input -> device, both ops with the real silu*mul between them, result -> host
+    out_host = torch.empty(rows, HIDDEN, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        xd = x_host.to(dev, non_blocking=True)
+        _, (a, b) = ns.fused_all_gather_matmul(xd, [w1, w3], 0, g, return_A=False)
+        hh = torch.nn.functional.silu(a).mul_(b)
+        o = ns.fused_matmul_reduce_scatter(hh, w2, "sum", 0, g)
+        out_host.copy_(o, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        e2e_step()
+    e1.record()
+    sync_all()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1) / K)
+    symm.sync_check()
+
+    if rank == 0:
+        peak_tf, peak_kind = _peaks()
+        tf_gpu = FLOPS_STEP / (ms_step * 1e-3) / 1e12
+        ag_tf = FLOPS_AG / (ms_ag * 1e-3) / 1e12
+        rs_tf = FLOPS_RS / (ms_rs * 1e-3) / 1e12
+        nv_bytes = (world - 1) / world * TOKENS * HIDDEN * 2  # both ops move this much per GPU
+        roof_ag = max(FLOPS_AG / NOMINAL_BF16, nv_bytes / NVLINK_BPS)
+        roof_rs = max(FLOPS_RS / NOMINAL_BF16, nv_bytes / NVLINK_BPS)
+        line = {
+            "metric": METRIC, "value": tf_gpu * world, "unit": "TFLOP/s", "n_gpus": world, "steps": K, "warmup": max(W, 3),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": _config(world, "gpu"),
+            "per_gpu_tflops": tf_gpu,
+            "ops": {
+                "ag_gemm": {"ms": ms_ag, "tflops_per_gpu": ag_tf, "frac_of_north_star_roofline": roof_ag * 1e3 / ms_ag,
+                            "bound": "tensor" if FLOPS_AG / NOMINAL_BF16 >= nv_bytes / NVLINK_BPS else "nvlink"},
+                "gemm_rs": {"ms": ms_rs, "tflops_per_gpu": rs_tf, "frac_of_north_star_roofline": roof_rs * 1e3 / ms_rs,
+                            "bound": "tensor" if FLOPS_RS / NOMINAL_BF16 >= nv_bytes / NVLINK_BPS else "nvlink"},
+                "nvlink_bytes_per_gpu_per_op": nv_bytes,
+            },
+            "roofline": {"bound": "tensor", "kernel": "gemm_fused_kernel<256,4,false> (all-gather mode)", "achieved": ag_tf,
+                         "peak": peak_tf, "unit": "TFLOP/s", "frac": ag_tf / peak_tf, "peak_kind": f"of {peak_kind} (sustained cuBLAS bf16)",
+                         "frac_of_nominal_2250": ag_tf / 2250.0, "traffic": TRAFFIC_AG_BYTES},
+            "e2e": {"value": world * FLOPS_STEP / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2},
+            "gpu_launches": int(launches) * world,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = {k: v for k, v in cpu_unfused(1, 3, 1).items() if k != "ms_per_step"}
+        print(json.dumps(line), flush=True)
+    symm.shutdown()
+    if world > 1:
+        dist.barrier()
+    dist.destroy_process_group()
+
+
+# DRAM bytes (read + write) of one all-gather-mode launch at this workload, from the ncu capture
+# summarised in profiles/; None until a capture exists.
+TRAFFIC_AG_BYTES = None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", "1")))
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (used for ncu captures)")
+    ap.add_argument("--tokens", type=int, default=TOKENS, help="total tokens (default: the BASELINE workload)")
+    args = ap.parse_args()
+    _set_tokens(args.tokens)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

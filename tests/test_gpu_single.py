@@ -1,0 +1,361 @@
+"""Parity of the sm_100a kernels on one GPU (a tensor-parallel group of one rank), called through
+torch.ops._ap_symm_mem -> ctypes -> the C ABI, checked against the CPU oracle and the golden
+fixtures. Tolerances are the ones the task states: relative Frobenius error <= 1e-2 for bf16
+with fp32 accumulation and <= 3e-2 for fp8, against an fp64 product of the same (already
+quantised) operands."""
+import ctypes as C
+import os
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+
+pytestmark = pytest.mark.gpu
+
+BF16_TOL = 1e-2
+FP8_TOL = 3e-2
+
+
+@pytest.fixture(scope="module")
+def group():
+    from autoparallel_b200.build import build_native
+    import autoparallel_b200.asynctp_ops  # noqa: F401  registers the ops
+    from autoparallel_b200 import symm
+
+    assert torch.cuda.is_available(), "gpu tests need a CUDA device"
+    build_native()
+    torch.cuda.set_device(0)
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    with tempfile.TemporaryDirectory() as d:
+        dist.init_process_group("gloo", init_method=f"file://{os.path.join(d, 'init')}", rank=0, world_size=1)
+        yield dist.group.WORLD.group_name
+        torch.cuda.synchronize()
+        symm.sync_check()
+        symm.shutdown()
+        dist.destroy_process_group()
+
+
+def _orc():
+    from oracle import asynctp_oracle as orc
+
+    return orc
+
+
+def _ag(A, Bs, gd, g, return_A=True):
+    A_out, outs = torch.ops._ap_symm_mem.fused_all_gather_matmul(A.cuda(), [b.cuda() for b in Bs], gd, g, return_A=return_A)
+    torch.cuda.synchronize()
+    return A_out, outs
+
+
+@pytest.mark.parametrize(
+    "rows,K,Ns",
+    [(128, 64, [256]), (1, 8, [8]), (127, 72, [8, 16]), (1000, 1032, [264, 128]), (384, 4096, [1792, 1792]),
+     (512, 512, [64, 128, 32]), (300, 200, [512, 128, 128, 40])],
+)
+@pytest.mark.parametrize("b_layout", ["row_major", "transposed_view"])
+def test_all_gather_matmul_shapes(group, rows, K, Ns, b_layout):
+    orc = _orc()
+    A = orc.activations(0, rows, K)
+    Bs = [orc.weights(7 + i, K, n) for i, n in enumerate(Ns)]
+    dev_Bs = [b.cuda() if b_layout == "row_major" else b.cuda().t().contiguous().t() for b in Bs]
+    A_out, outs = torch.ops._ap_symm_mem.fused_all_gather_matmul(A.cuda(), dev_Bs, 0, group)
+    torch.cuda.synchronize()
+    A_ref, outs_ref = orc.all_gather_matmul_local([A], Bs, 0)
+    assert torch.equal(A_out.cpu(), A_ref)
+    for o, o_ref, b in zip(outs, outs_ref, Bs):
+        assert o.shape == o_ref.shape and o.dtype == o_ref.dtype
+        assert not torch.isnan(o).any()
+        ref64 = A.double() @ b.double()
+        assert orc.rel_fro_error(o, ref64) <= BF16_TOL
+        # and as close to fp64 as the reference decomposition itself (bf16 output rounding)
+        assert orc.rel_fro_error(o, ref64) <= 1.5 * orc.rel_fro_error(o_ref, ref64) + 1e-4
+
+
+def test_all_gather_matmul_nd_and_return_A(group):
+    orc = _orc()
+    A = orc.activations(3, 4 * 6, 64).view(4, 6, 64)
+    Bs = [orc.weights(7, 64, 40), orc.weights(8, 64, 24)]
+    for gd in (0, 1):
+        for return_A in (True, False):
+            A_out, outs = _ag(A, Bs, gd, group, return_A)
+            A_ref, outs_ref = orc.all_gather_matmul_local([A], Bs, gd, return_A)
+            assert (A_out is None) == (not return_A)
+            if return_A:
+                assert torch.equal(A_out.cpu(), A_ref)
+            for o, o_ref in zip(outs, outs_ref):
+                assert o.shape == o_ref.shape
+                assert orc.rel_fro_error(o, o_ref.double()) <= BF16_TOL
+    # a strided A (gather_dim not in front in memory) is accepted, like the reference
+    A_nc = A.transpose(0, 1).contiguous().transpose(0, 1)
+    _, outs = _ag(A_nc, Bs, 0, group)
+    _, outs_ref = orc.all_gather_matmul_local([A], Bs, 0)
+    assert orc.rel_fro_error(outs[0], outs_ref[0].double()) <= BF16_TOL
+
+
+def test_golden_all_gather_matmul(group, golden):
+    """bf16 golden cases: the gathered A the reference produced, times the Bs, must give its outputs."""
+    orc = _orc()
+    n = 0
+    for rec in golden["ranks"][0]:
+        if rec["kind"] != "ag_mm" or rec["dtype"] != "torch.bfloat16" or rec["gather_dim"] == len(rec["shape"]) - 1:
+            continue
+        gd = rec["gather_dim"]
+        _, outs = _ag(rec["A_out"], rec["Bs"], gd, group, return_A=False)
+        for o, gold in zip(outs, rec["outs"]):
+            assert o.shape == gold.shape
+            torch.testing.assert_close(o.cpu().float(), gold.float(), rtol=2 ** -7, atol=2e-3)
+        n += 1
+    assert n == 3
+
+
+def test_golden_matmul_reduce_scatter_partials(group, golden):
+    """Each rank's partial comes from the kernel (group of one); summed like the reference they give its output."""
+    r0, r1 = golden["ranks"]
+    n = 0
+    for c0, c1 in zip(r0, r1):
+        if c0["kind"] != "mm_rs" or c0["dtype"] != "torch.bfloat16" or c0["scatter_dim"] != 0:
+            continue
+        parts = [
+            torch.ops._ap_symm_mem.fused_matmul_reduce_scatter(c["A"].cuda(), c["B"].cuda(), "sum", 0, group).float().cpu()
+            for c in (c0, c1)
+        ]
+        total = parts[0] + parts[1]
+        if c0["op"] == "avg":
+            total = total / 2
+        for rank, c in enumerate((c0, c1)):
+            mine = total.chunk(2, dim=0)[rank]
+            torch.testing.assert_close(mine, c["out"].float(), rtol=2 ** -6, atol=4e-3)
+        n += 1
+    assert n == 4
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 64, 256), (1000, 520, 264), (2048, 1792, 4096), (64, 128, 8)])
+@pytest.mark.parametrize("op", ["sum", "avg"])
+def test_matmul_reduce_scatter_single_rank(group, M, K, N, op):
+    orc = _orc()
+    A, B = orc.activations(1, M, K), orc.weights(9, K, N)
+    out = torch.ops._ap_symm_mem.fused_matmul_reduce_scatter(A.cuda(), B.cuda(), op, 0, group)
+    torch.cuda.synchronize()
+    (ref,) = orc.matmul_reduce_scatter_local([A], [B], op, 0)
+    assert out.shape == ref.shape and out.dtype == ref.dtype
+    assert orc.rel_fro_error(out, A.double() @ B.double()) <= BF16_TOL
+
+
+def test_matmul_reduce_scatter_3d(group):
+    orc = _orc()
+    A = orc.activations(2, 4 * 6, 64).view(4, 6, 64)
+    B = orc.weights(9, 64, 40)
+    for sd in (0, 1):
+        out = torch.ops._ap_symm_mem.fused_matmul_reduce_scatter(A.cuda(), B.cuda(), "sum", sd, group)
+        (ref,) = orc.matmul_reduce_scatter_local([A], [B], "sum", sd)
+        assert out.shape == ref.shape
+        assert orc.rel_fro_error(out, (A.double() @ B.double())) <= BF16_TOL
+
+
+def test_empty_and_errors(group):
+    bf = torch.bfloat16
+    A = torch.empty(0, 64, dtype=bf, device="cuda")
+    B = torch.zeros(64, 16, dtype=bf, device="cuda")
+    A_out, (o,) = torch.ops._ap_symm_mem.fused_all_gather_matmul(A, [B], 0, group)
+    assert A_out.shape == (0, 64) and o.shape == (0, 16)
+    out = torch.ops._ap_symm_mem.fused_matmul_reduce_scatter(A, B, "sum", 0, group)
+    assert out.shape == (0, 16)
+    X = torch.zeros(8, 64, dtype=bf, device="cuda")
+    with pytest.raises(ValueError, match="reduce_op must be sum or avg"):
+        torch.ops._ap_symm_mem.fused_matmul_reduce_scatter(X, B, "max", 0, group)
+    with pytest.raises(ValueError, match="Invalid gather_dim"):
+        torch.ops._ap_symm_mem.fused_all_gather_matmul(X, [B], 3, group)
+    with pytest.raises(NotImplementedError, match="bfloat16 or float8_e4m3fn"):
+        torch.ops._ap_symm_mem.fused_all_gather_matmul(X.float(), [B.float()], 0, group)
+    from autoparallel_b200._native import ApkError
+
+    with pytest.raises(ApkError, match="multiple of"):  # N = 12 cannot be stored in 16-byte vectors
+        torch.ops._ap_symm_mem.fused_all_gather_matmul(X, [torch.zeros(64, 12, dtype=bf, device="cuda")], 0, group)
+
+
+# --------------------------------------------------------------------------------------- fp8
+def _fp8_case(orc, rows, K, N, seed=0):
+    x = orc.activations(seed, rows, K, torch.float32)
+    w = orc.weights(seed + 7, K, N, torch.float32)
+    a8, sa = orc.quantize_rowwise(x, 1)
+    b8, sb = orc.quantize_rowwise(w, 0)
+    return a8, sa, b8, sb
+
+
+@pytest.mark.parametrize("rows,K,N", [(128, 128, 256), (1000, 1040, 264), (2048, 8192, 3584), (5, 16, 8)])
+def test_scaled_all_gather_matmul_rowwise(group, rows, K, N):
+    orc = _orc()
+    a8, sa, b8, sb = _fp8_case(orc, rows, K, N)
+    b_dev = b8.cuda().t().contiguous().t()  # column-major, as _scaled_mm requires
+    A_out, (o,) = torch.ops._ap_symm_mem.fused_all_gather_scaled_matmul(
+        a8.cuda(), [b_dev], sa.cuda(), [sb.cuda()], 0, group, [None], [None], [torch.bfloat16], [False]
+    )
+    torch.cuda.synchronize()
+    assert torch.equal(A_out.cpu().view(torch.uint8), a8.view(torch.uint8))
+    ref64 = (a8.double() * sa.double()) @ (b8.double() * sb.double())
+    assert o.dtype == torch.bfloat16 and orc.rel_fro_error(o, ref64) <= FP8_TOL
+    _, (o_ref,) = orc.all_gather_scaled_matmul_local([a8], [b8], [sa], [sb], 0, [None], [None], [torch.bfloat16])
+    torch.testing.assert_close(o.cpu().float(), o_ref.float(), rtol=2 ** -7, atol=1e-3)
+    # the oracle's restatement of row-wise scaling agrees with torch._scaled_mm on this GPU
+    if K % 16 == 0 and N % 16 == 0:
+        lib_out = torch._scaled_mm(a8.cuda(), b_dev, sa.cuda(), sb.cuda(), out_dtype=torch.bfloat16)
+        torch.testing.assert_close(lib_out.cpu().float(), o_ref.float(), rtol=2 ** -6, atol=2e-3)
+
+
+def test_scaled_all_gather_matmul_scale_modes_bias_result_scale(group):
+    orc = _orc()
+    a8, sa, b8, sb = _fp8_case(orc, 256, 256, 128, seed=3)
+    b_dev = b8.cuda().t().contiguous().t()
+    bias = orc.weights(99, 1, 128, torch.bfloat16, std=1.0).view(-1)
+    rs = torch.tensor(0.5)
+    t = torch.tensor(0.25)
+    for a_scale in (sa, t):
+        for out_dtype in (torch.bfloat16, torch.float32):
+            _, (o,) = torch.ops._ap_symm_mem.fused_all_gather_scaled_matmul(
+                a8.cuda(), [b_dev], a_scale.cuda(), [sb.cuda()], 0, group, [bias.cuda()], [rs.cuda()], [out_dtype], [True]
+            )
+            _, (o_ref,) = orc.all_gather_scaled_matmul_local(
+                [a8], [b8], [a_scale], [sb], 0, [bias], [rs], [out_dtype], compute_dtype=torch.float64
+            )
+            assert o.dtype == out_dtype
+            assert orc.rel_fro_error(o, o_ref.double()) <= (FP8_TOL if out_dtype == torch.bfloat16 else 1e-5)
+
+
+@pytest.mark.parametrize("op", ["sum", "avg"])
+def test_scaled_matmul_reduce_scatter_single_rank(group, op):
+    orc = _orc()
+    a8, sa, b8, sb = _fp8_case(orc, 512, 384, 264, seed=5)
+    b_dev = b8.cuda().t().contiguous().t()
+    out = torch.ops._ap_symm_mem.fused_scaled_matmul_reduce_scatter(
+        a8.cuda(), b_dev, sa.cuda(), sb.cuda(), op, 0, 0, group, [512, 264], None, None, torch.bfloat16, False
+    )
+    (ref,) = orc.scaled_matmul_reduce_scatter_local([a8], [b8], [sa], [sb], op, 0, [512, 264], out_dtype=torch.bfloat16)
+    assert out.shape == ref.shape and out.dtype == ref.dtype
+    ref64 = (a8.double() * sa.double()) @ (b8.double() * sb.double())
+    assert orc.rel_fro_error(out, ref64) <= FP8_TOL
+
+
+# --------------------------------------------------------------------------------------- full size
+def _freivalds(out, A, B, tol):
+    """C x == A (B x) for random x, in fp64 on the device: an O(MN) check of a product of any size."""
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(out.shape[1], 4, device="cuda", dtype=torch.float64, generator=g)
+    lhs = out.double() @ x
+    rhs = A.double() @ (B.double() @ x)
+    err = ((lhs - rhs).norm() / rhs.norm()).item()
+    assert err <= tol, err
+
+
+def test_full_size_llama8b_mlp_properties(group):
+    """BASELINE config 2 on one rank: 32768 tokens x 4096, w1/w3 [4096,1792], w2 [1792,4096]."""
+    torch.manual_seed(0)
+    A = torch.randn(32768, 4096, device="cuda").bfloat16()
+    w1 = (torch.randn(4096, 1792, device="cuda") * 0.02).bfloat16()
+    w3 = (torch.randn(4096, 1792, device="cuda") * 0.02).bfloat16()
+    _, (h1, h3) = torch.ops._ap_symm_mem.fused_all_gather_matmul(A, [w1, w3], 0, group, return_A=False)
+    _freivalds(h1, A, w1, BF16_TOL)
+    _freivalds(h3, A, w3, BF16_TOL)
+    # column sums: 1^T C == (1^T A) B
+    torch.testing.assert_close(h1.double().sum(0), A.double().sum(0) @ w1.double(), rtol=1e-2, atol=0.5)
+    h = torch.nn.functional.silu(h1.float()).mul_(h3.float()).bfloat16()
+    w2 = (torch.randn(1792, 4096, device="cuda") * 0.02).bfloat16()
+    out = torch.ops._ap_symm_mem.fused_matmul_reduce_scatter(h, w2, "sum", 0, group)
+    assert out.shape == (32768, 4096)
+    _freivalds(out, h, w2, BF16_TOL)
+    # idempotence: the same call gives the same bits
+    out2 = torch.ops._ap_symm_mem.fused_matmul_reduce_scatter(h, w2, "sum", 0, group)
+    assert torch.equal(out, out2)
+
+
+def test_full_size_llama70b_fp8_properties(group):
+    """BASELINE config 4 on one rank: 16384 tokens x 8192 e4m3 row-wise, w1 [8192,3584]."""
+    orc = _orc()
+    torch.manual_seed(1)
+    x = torch.randn(16384, 8192, device="cuda")
+    w = torch.randn(8192, 3584, device="cuda") * 0.02
+    sa = x.abs().amax(1, keepdim=True) / 448
+    sb = w.abs().amax(0, keepdim=True) / 448
+    a8 = (x / sa).to(orc.FP8)
+    b8 = (w / sb).to(orc.FP8).t().contiguous().t()
+    _, (o,) = torch.ops._ap_symm_mem.fused_all_gather_scaled_matmul(
+        a8, [b8], sa, [sb], 0, group, [None], [None], [torch.bfloat16], [False]
+    )
+    g = torch.Generator(device="cuda").manual_seed(5)
+    v = torch.randn(3584, 4, device="cuda", dtype=torch.float64, generator=g)
+    lhs = o.double() @ v
+    rhs = (a8.double() * sa.double()) @ ((b8.double() * sb.double()) @ v)
+    assert ((lhs - rhs).norm() / rhs.norm()).item() <= FP8_TOL
+
+
+# --------------------------------------------------------------------------------------- C ABI, status word
+def test_c_abi_direct_call_and_alignment_error(group):
+    from autoparallel_b200 import _native as nat
+
+    L = nat.lib()
+    orc = _orc()
+    A = orc.activations(0, 256, 128).cuda()
+    B = orc.weights(7, 128, 64).cuda()
+    out = torch.empty(256, 64, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    comm = nat.ApkComm()
+    comm.rank, comm.world, comm.status, comm.epoch, comm.timeout_s = 0, 1, status.data_ptr(), 1, 5.0
+    args = nat.ApkAgGemmArgs()
+    args.dtype, args.rows_per_rank, args.K, args.nB = nat.APK_BF16, 256, 128, 1
+    args.A_shard, args.lda = A.data_ptr(), 128
+    op = args.Bs[0]
+    op.B, op.ldb, op.n_major, op.N = B.data_ptr(), 64, 1, 64
+    op.out, op.ldo, op.out_dtype = out.data_ptr(), 64, nat.APK_BF16
+    before = L.apk_launch_count()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert L.apk_ag_gemm(C.byref(comm), C.byref(args), stream) == nat.APK_OK
+    assert L.apk_launch_count() == before + 1
+    raw = C.c_uint32(7)
+    assert L.apk_check_status(C.byref(comm), stream, C.byref(raw)) == nat.APK_OK and raw.value == 0
+    assert orc.rel_fro_error(out, A.double().cpu() @ B.double().cpu()) <= BF16_TOL
+    args.A_shard = A.data_ptr() + 2  # not 16-byte aligned: rejected before any launch
+    assert L.apk_ag_gemm(C.byref(comm), C.byref(args), stream) == nat.APK_ERR_ARG
+    assert b"16-byte aligned" in L.apk_last_error()
+
+
+def test_device_wait_times_out_cleanly(group):
+    """A two-rank reduce-scatter whose 'peer' is this GPU's own memory and never answers: the
+    wait for the peer's partial runs out after timeout_s, the kernel frees its resources and
+    returns, the status word says which wait gave up, and the context stays usable."""
+    from autoparallel_b200 import _native as nat
+
+    L = nat.lib()
+    orc = _orc()
+    M, K, N = 256, 64, 64
+    A = orc.activations(0, M, K).cuda()
+    B = orc.weights(7, K, N).cuda()
+    out = torch.empty(M // 2, N, dtype=torch.bfloat16, device="cuda")
+    arena = torch.zeros(2 * M * N, dtype=torch.bfloat16, device="cuda")
+    flags = torch.zeros(8192 * 2, dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ctrl = torch.zeros(1024, dtype=torch.int32, device="cuda")
+    comm = nat.ApkComm()
+    comm.rank, comm.world = 0, 2
+    for r in range(2):
+        comm.data[r] = arena.data_ptr()
+        comm.flags[r] = flags.data_ptr()
+    comm.data_bytes, comm.flag_bytes = arena.numel() * 2, flags.numel() * 4
+    comm.ctrl, comm.ctrl_bytes = ctrl.data_ptr(), ctrl.numel() * 4
+    comm.status, comm.epoch, comm.timeout_s = status.data_ptr(), 1, 0.2
+    args = nat.ApkGemmRsArgs()
+    args.dtype, args.M, args.K, args.reduce_op = nat.APK_BF16, M, K, nat.APK_REDUCE_SUM
+    args.A, args.lda = A.data_ptr(), K
+    args.B.B, args.B.ldb, args.B.n_major, args.B.N = B.data_ptr(), N, 1, N
+    args.B.out, args.B.ldo, args.B.out_dtype = out.data_ptr(), N, nat.APK_BF16
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert L.apk_gemm_rs(C.byref(comm), C.byref(args), stream) == nat.APK_OK
+    raw = C.c_uint32(0)
+    assert L.apk_check_status(C.byref(comm), stream, C.byref(raw)) == nat.APK_ERR_TIMEOUT
+    assert raw.value & 0xFF == 4 and raw.value >> 8 == 1  # peer partial, source rank 1
+    assert b"peer partial" in L.apk_last_error()
+    # the partial for the other rank was still produced, and the device still works
+    part = arena[: (M // 2) * N].view(M // 2, N)
+    assert orc.rel_fro_error(part, (A.double().cpu() @ B.double().cpu())[M // 2:]) <= BF16_TOL
+    assert L.apk_check_status(C.byref(comm), stream, C.byref(raw)) == nat.APK_OK
+    assert float((A.float() @ B.float()).sum()) == float((A.float() @ B.float()).sum())
