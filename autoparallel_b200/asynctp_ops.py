@@ -374,7 +374,7 @@ def _ag_gemm_native(
     M = rows * world
 
     def unflatten(t: torch.Tensor) -> torch.Tensor:
-        return t.view(*lead, -1).flatten(0, 1).movedim(0, gather_dim)
+        return t.view(*lead, t.shape[-1]).flatten(0, 1).movedim(0, gather_dim)
 
     outs = [A2.new_empty((M, B.shape[1]), dtype=od or B.dtype) for B, od in zip(Bs, out_dtypes)]
     need_gathered = world > 1 or return_A
@@ -562,7 +562,7 @@ def _fused_matmul_reduce_scatter(
             raise ValueError(f"dim {scatter_dim} of A ({lead[0]}) is not divisible by the group size {world}")
         lead[0] //= world
         out = _gemm_rs_native(fronted.flatten(0, -2), B, None, None, None, None, A.dtype, reduce_op, group_name)
-        return out.view(*lead, -1).movedim(0, scatter_dim)
+        return out.view(*lead, B.shape[1]).movedim(0, scatter_dim)
 
 
 @torch.library.impl(lib, "fused_scaled_matmul_reduce_scatter", "CUDA")
@@ -625,7 +625,7 @@ def _fused_scaled_matmul_reduce_scatter(
         final_shape = list(output_shape)
         final_shape[-1] = B.shape[1]
         final_shape[orig_scatter_dim] //= world
-        return out.view(*lead, -1).movedim(0, sd).reshape(final_shape)
+        return out.view(*lead, B.shape[1]).movedim(0, sd).reshape(final_shape)
 
 
 @torch.library.impl(lib, "_low_contention_all_gather", "Meta")

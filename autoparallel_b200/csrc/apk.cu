@@ -145,7 +145,7 @@ int launch(const apk::KParams& kp, int max_n, bool fp8, cudaStream_t stream) {
 
 uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
 
-int fill_operand(apk::KParams* kp, int b, const apk_operand& op, int dtype, int K, int bn, const char* what) {
+int fill_operand(apk::KParams* kp, int b, const apk_operand& op, int dtype, int K, int bn, int64_t out_rows, const char* what) {
   if (op.B == nullptr || op.out == nullptr) return fail(APK_ERR_ARG, "%s: null B or out", what);
   if (op.N <= 0) return fail(APK_ERR_ARG, "%s: N must be positive", what);
   if (op.out_dtype != APK_BF16 && op.out_dtype != APK_F32) return fail(APK_ERR_ARG, "%s: out dtype must be bf16 or f32", what);
@@ -167,6 +167,12 @@ int fill_operand(apk::KParams* kp, int b, const apk_operand& op, int dtype, int 
   kp->out[b] = op.out;
   kp->ldo[b] = op.ldo;
   kp->out_fp32[b] = op.out_dtype == APK_F32;
+  if (op.out_dtype == APK_BF16) {
+    // stores: 32 rows x 64 columns per TMA instruction, clipped at N by the descriptor
+    rc = encode_2d(&kp->tmOut[b], APK_BF16, op.out, (uint64_t)op.N, (uint64_t)out_rows, (uint64_t)op.ldo, 64, 32, what);
+    if (rc != APK_OK) return rc;
+    kp->out_tma[b] = 1;
+  }
   if (op.b_scale_mode != APK_SCALE_NONE && op.b_scale_mode != APK_SCALE_SCALAR && op.b_scale_mode != APK_SCALE_VECTOR)
     return fail(APK_ERR_ARG, "%s: bad b_scale_mode", what);
   if (op.b_scale_mode != APK_SCALE_NONE && op.b_scale == nullptr) return fail(APK_ERR_ARG, "%s: b_scale is null", what);
@@ -264,7 +270,9 @@ uint64_t apk_ag_gemm_arena_bytes(const apk_ag_gemm_args* a, int32_t world) {
 uint64_t apk_gemm_rs_arena_bytes(const apk_gemm_rs_args* a, int32_t world) {
   if (a == nullptr || world <= 1) return 0;
   const uint64_t oes = a->B.out_dtype == APK_F32 ? 4 : 2;
-  return align_up((uint64_t)a->M * (uint64_t)a->B.N * oes, 256);
+  // one slot per source rank, each padded to whole 128-row tiles
+  const uint64_t slot_rows = align_up((uint64_t)(a->M / world), apk::BM);
+  return align_up((uint64_t)world * slot_rows * (uint64_t)a->B.N * oes, 256);
 }
 
 uint64_t apk_ctrl_bytes(int32_t rows_per_rank, int32_t world) {
@@ -314,7 +322,7 @@ int apk_ag_gemm(const apk_comm* comm, const apk_ag_gemm_args* a, void* stream_) 
     if (rc != APK_OK) return rc;
   }
   for (int b = 0; b < a->nB; ++b) {
-    rc = fill_operand(&kp, b, a->Bs[b], a->dtype, a->K, bn, "Bs[i]");
+    rc = fill_operand(&kp, b, a->Bs[b], a->dtype, a->K, bn, M, "Bs[i]");
     if (rc != APK_OK) return rc;
   }
   // A scale
@@ -399,12 +407,13 @@ int apk_gemm_rs(const apk_comm* comm, const apk_gemm_rs_args* a, void* stream_) 
   kp.M = a->M;
   kp.K = a->K;
   kp.rows_per_rank = a->M / ws;
+  kp.rs_slot_rows = (int32_t)align_up((uint64_t)kp.rows_per_rank, apk::BM);
   kp.elem_bytes = es;
   const int bn = a->B.N <= 128 ? 128 : 256;
   const int bke = a->dtype == APK_BF16 ? 64 : 128;
   rc = encode_2d(&kp.tmA0, a->dtype, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, bke, apk::BM, "A");
   if (rc != APK_OK) return rc;
-  rc = fill_operand(&kp, 0, a->B, a->dtype, a->K, bn, "B");
+  rc = fill_operand(&kp, 0, a->B, a->dtype, a->K, bn, a->M / ws, "B");
   if (rc != APK_OK) return rc;
   switch (a->a_scale_mode) {
     case APK_SCALE_NONE:
@@ -434,11 +443,19 @@ int apk_gemm_rs(const apk_comm* comm, const apk_gemm_rs_args* a, void* stream_) 
     const uint64_t tiles = (uint64_t)((kp.rows_per_rank + apk::BM - 1) / apk::BM) * (uint64_t)((a->B.N + bn - 1) / bn);
     if (tiles > max_tiles) return fail(APK_ERR_SIZE, "signal pad holds %llu tile flags per rank, need %llu", (unsigned long long)max_tiles, (unsigned long long)tiles);
     kp.rs_max_tiles = (int32_t)max_tiles;
+    kp.rs_slot_rows = (int32_t)align_up((uint64_t)kp.rows_per_rank, apk::BM);
     const uint64_t off = (comm->epoch & 1u) ? half : 0;
+    if ((half & 15u) != 0) return fail(APK_ERR_ARG, "arena halves must be 16-byte aligned");
     for (int r = 0; r < ws; ++r) {
       kp.rs_arena_peer[r] = reinterpret_cast<uint8_t*>(comm->data[r]) + off;
       kp.rs_flag_peer[r] = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(comm->flags[r]) + kFlagRsOffset);
+      if (a->B.out_dtype == APK_BF16 && r != comm->rank) {
+        rc = encode_2d(&kp.tmArena[r], APK_BF16, kp.rs_arena_peer[r], (uint64_t)a->B.N, (uint64_t)ws * kp.rs_slot_rows,
+                       (uint64_t)a->B.N, 64, 32, "peer arena");
+        if (rc != APK_OK) return rc;
+      }
     }
+    kp.rs_arena_tma = a->B.out_dtype == APK_BF16;
     kp.rs_arena_local = kp.rs_arena_peer[comm->rank];
     kp.rs_flag_local = kp.rs_flag_peer[comm->rank];
   }

@@ -56,6 +56,8 @@ struct alignas(64) KParams {
   CUtensorMap tmA0;            // plain / RS: all of A. AG: the local shard [rows_per_rank, K]
   CUtensorMap tmA1;            // AG: the gathered A [M, K]
   CUtensorMap tmB[MAX_B];
+  CUtensorMap tmOut[MAX_B];            // bf16 outputs, box 32 rows x 64 columns (TMA stores)
+  CUtensorMap tmArena[MAX_WORLD];      // RS: every peer's arena half as [ws * rs_slot_rows, N]
   int32_t mode, ws, rank, nB;
   int32_t M, K, rows_per_rank, elem_bytes;
   int32_t N[MAX_B];
@@ -63,6 +65,7 @@ struct alignas(64) KParams {
   void* out[MAX_B];
   int64_t ldo[MAX_B];
   int32_t out_fp32[MAX_B];
+  int32_t out_tma[MAX_B];      // tmOut[b] is valid
   // ---- scaled (fp8) epilogue
   int32_t a_scale_mode;        // 0 none, 1 one scalar, 2 one per row
   const float* a_scale_own;    // AG row-wise-sharded: scales of the local shard's rows
@@ -88,11 +91,13 @@ struct alignas(64) KParams {
   uint32_t* ready;                     // [ws * tiles_m_per_chunk] local counters, zeroed per call
   uint32_t* ctrl;                      // local scratch counters, zeroed per call
   // ---- reduce-scatter
-  uint8_t* rs_arena_local;             // [ws][rows_per_rank][N] partials (current parity)
+  uint8_t* rs_arena_local;             // [ws][rs_slot_rows][N] partials (current parity)
   uint8_t* rs_arena_peer[MAX_WORLD];
   uint32_t* rs_flag_local;             // [ws][rs_max_tiles]
   uint32_t* rs_flag_peer[MAX_WORLD];
   int32_t rs_max_tiles;
+  int32_t rs_slot_rows;                // rows_per_rank rounded up to whole 128-row tiles
+  int32_t rs_arena_tma;                // tmArena[] are valid
   float reduce_scale;                  // 1 for sum, 1/ws for avg
   // ---- common
   uint32_t epoch;
@@ -105,7 +110,9 @@ struct SmemLayout {
   static constexpr int A_BYTES = BM * ROW_BYTES;
   static constexpr int B_BYTES = BN * ROW_BYTES;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
+  static constexpr int STG_OFF = STAGES * STAGE_BYTES;              // epilogue staging, 1024-aligned
+  static constexpr int STG_WARP_BYTES = 2 * 32 * ROW_BYTES;         // two 32-row x 128-byte buffers per warp
+  static constexpr int BAR_OFF = STG_OFF + EPI_WARPS * STG_WARP_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 5;
   static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
   static constexpr int TOTAL = MISC_OFF + 16 + 1024;  // + alignment slack
@@ -477,6 +484,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
     const int quarter = warp & 3;                   // TMEM lanes this warp may read
     const int row_in_tile = quarter * 32 + lane;
     const bool epi_leader = (warp == 2 && lane == 0);
+    const uint32_t stg_base = smem_base + L::STG_OFF + (warp - 2) * L::STG_WARP_BYTES;
+    uint32_t stg_count = 0;
     uint32_t lt = 0;
     for (int t = blockIdx.x; t < sched.total_tiles; t += gridDim.x, ++lt) {
       const TileInfo ti = decode_tile<BN>(p, sched, t);
@@ -487,24 +496,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       const long long grow = (long long)ti.chunk * p.rows_per_rank + chunk_row;  // row of the full matrix
       const int b = ti.b;
       const bool own = (p.mode != MODE_RS) || (ti.chunk == p.rank);
-
-      // Row / tile constants of the scaled epilogue.
-      float sa = 1.0f;
-      if (p.a_scale_mode == 1) {
-        sa = __ldg(p.a_scale_full);
-      } else if (p.a_scale_mode == 2 && row_ok) {
-        if (p.mode == MODE_AG && p.a_scale_own != nullptr) {
-          sa = (ti.chunk == p.rank) ? __ldg(p.a_scale_own + chunk_row) : __ldcg(p.ag_scale_gathered + grow);
-        } else {
-          sa = __ldg(p.a_scale_full + grow);
-        }
-      }
-      const float* bs = p.b_scale[b];
-      const int bs_mode = p.b_scale_mode[b];
-      if (bs_mode == 1) sa *= __ldg(bs);
-      const float rscale = (p.result_scale[b] != nullptr) ? __ldg(p.result_scale[b]) : 1.0f;
-      const void* bias = p.bias[b];
-      const bool scaled = (p.a_scale_mode != 0) || (bs_mode != 0) || (bias != nullptr) || (p.result_scale[b] != nullptr);
 
       // One thread does the waiting (peers' partials for a tile this rank owns, then the
       // accumulator); its verdict is shared so that all four warps leave the loop together.
@@ -524,57 +515,121 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       if (epi_verdict[lt & 1u] == 0u) break;
       ptx::tc_fence_after();
 
+      // Row / tile constants of the scaled epilogue. Read only now: the gathered row scales of a
+      // peer's chunk are in place once the accumulator that consumed those rows is complete.
+      float sa = 1.0f;
+      if (p.a_scale_mode == 1) {
+        sa = __ldg(p.a_scale_full);
+      } else if (p.a_scale_mode == 2 && row_ok) {
+        if (p.mode == MODE_AG && p.a_scale_own != nullptr) {
+          sa = (ti.chunk == p.rank) ? __ldg(p.a_scale_own + chunk_row) : __ldcg(p.ag_scale_gathered + grow);
+        } else {
+          sa = __ldg(p.a_scale_full + grow);
+        }
+      }
+      const float* bs = p.b_scale[b];
+      const int bs_mode = p.b_scale_mode[b];
+      if (bs_mode == 1) sa *= __ldg(bs);
+      const float rscale = (p.result_scale[b] != nullptr) ? __ldg(p.result_scale[b]) : 1.0f;
+      const void* bias = p.bias[b];
+      const bool scaled = (p.a_scale_mode != 0) || (bs_mode != 0) || (bias != nullptr) || (p.result_scale[b] != nullptr);
+
+
       const bool o32 = p.out_fp32[b] != 0;
       const int oes = o32 ? 4 : 2;
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+      const bool rs_remote = (p.mode == MODE_RS) && !own;
+      // Stores go through shared memory and TMA (full 128-byte rows, also over NVLink) whenever
+      // TMA's clipping is enough: bf16, and either all 128 rows exist or the rows past the end
+      // land in the padding of this rank's arena slot.
+      const bool use_tma = rs_remote ? (p.rs_arena_tma != 0) : (p.out_tma[b] != 0 && ti.rows_valid == BM);
+      const CUtensorMap* tm_st = rs_remote ? &p.tmArena[ti.chunk] : &p.tmOut[b];
+      int st_row;  // first row this warp stores, in the coordinates of tm_st
+      if (rs_remote) {
+        st_row = p.rank * p.rs_slot_rows + ti.mt * BM + quarter * 32;
+      } else if (p.mode == MODE_RS) {
+        st_row = ti.mt * BM + quarter * 32;
+      } else {
+        st_row = ti.chunk * p.rows_per_rank + ti.mt * BM + quarter * 32;
+      }
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        if (c * 32 >= ti.n_valid) break;   // uniform across the warp
-        uint32_t raw[32];
-        ptx::tmem_ld_32x32(t_row + c * 32, raw);
-        ptx::tmem_ld_wait();
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
-        const int col0 = ti.n0 + c * 32;
-        const int nvalid = min(32, p.N[b] - col0);
-        if (scaled) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float x = v[j] * sa;
-            if (j < nvalid) {
-              if (bs_mode == 2) x *= __ldg(bs + col0 + j);
-              if (bias != nullptr) {
-                x += p.bias_fp32[b] ? __ldg(reinterpret_cast<const float*>(bias) + col0 + j)
-                                    : __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(bias) + col0 + j));
-              }
-            }
-            v[j] = x * rscale;
-          }
+      for (int g = 0; g < BN / 64; ++g) {
+        if (g * 64 >= ti.n_valid) break;   // uniform across the warp
+        const uint32_t stg = stg_base + (stg_count & 1u) * (32 * ROW_BYTES);
+        if (use_tma) {
+          // the store that last used this buffer must have finished reading it
+          if (lane == 0) ptx::bulk_wait_group_read<1>();
+          __syncwarp();
         }
-        if (row_ok) {
-          if (p.mode != MODE_RS) {
-            uint8_t* dst = reinterpret_cast<uint8_t*>(p.out[b]) + ((size_t)grow * p.ldo[b] + col0) * oes;
-            store_row32(dst, v, nvalid, o32);
-          } else if (!own) {
-            // Partial for another rank: straight into its arena, slot = this rank.
-            uint8_t* dst = p.rs_arena_peer[ti.chunk] +
-                           (((size_t)p.rank * p.rows_per_rank + chunk_row) * p.N[b] + col0) * oes;
-            store_row32(dst, v, nvalid, o32);
-          } else {
-            for (int src = 0; src < p.ws; ++src) {
-              if (src == p.rank) continue;
-              const uint8_t* part = p.rs_arena_local +
-                                    (((size_t)src * p.rows_per_rank + chunk_row) * p.N[b] + col0) * oes;
-              add_row32(part, v, nvalid, o32);
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int c = g * 2 + hf;
+          if (c * 32 >= ti.n_valid) break;
+          uint32_t raw[32];
+          ptx::tmem_ld_32x32(t_row + c * 32, raw);
+          ptx::tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+          const int col0 = ti.n0 + c * 32;
+          const int nvalid = min(32, p.N[b] - col0);
+          if (scaled) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float x = v[j] * sa;
+              if (j < nvalid) {
+                if (bs_mode == 2) x *= __ldg(bs + col0 + j);
+                if (bias != nullptr) {
+                  x += p.bias_fp32[b] ? __ldg(reinterpret_cast<const float*>(bias) + col0 + j)
+                                      : __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(bias) + col0 + j));
+                }
+              }
+              v[j] = x * rscale;
+            }
+          }
+          if (p.mode == MODE_RS && own) {
+            if (row_ok) {
+              for (int src = 0; src < p.ws; ++src) {
+                if (src == p.rank) continue;
+                const uint8_t* part = p.rs_arena_local +
+                                      (((size_t)src * p.rs_slot_rows + chunk_row) * p.N[b] + col0) * oes;
+                add_row32(part, v, nvalid, o32);
+              }
             }
             if (p.reduce_scale != 1.0f) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] *= p.reduce_scale;
             }
-            uint8_t* dst = reinterpret_cast<uint8_t*>(p.out[b]) + ((size_t)chunk_row * p.ldo[b] + col0) * oes;
+          }
+          if (use_tma) {
+            // 16-byte chunk j of this thread's row goes where the 128-byte swizzle expects it
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t chunk = (uint32_t)(hf * 4 + j) ^ (uint32_t)(lane & 7);
+              ptx::st_shared_v4(stg + lane * ROW_BYTES + chunk * 16,
+                                pack_bf16(v[8 * j + 0], v[8 * j + 1]), pack_bf16(v[8 * j + 2], v[8 * j + 3]),
+                                pack_bf16(v[8 * j + 4], v[8 * j + 5]), pack_bf16(v[8 * j + 6], v[8 * j + 7]));
+            }
+          } else if (row_ok) {
+            uint8_t* dst;
+            if (rs_remote) {
+              dst = p.rs_arena_peer[ti.chunk] + (((size_t)p.rank * p.rs_slot_rows + chunk_row) * p.N[b] + col0) * oes;
+            } else if (p.mode == MODE_RS) {
+              dst = reinterpret_cast<uint8_t*>(p.out[b]) + ((size_t)chunk_row * p.ldo[b] + col0) * oes;
+            } else {
+              dst = reinterpret_cast<uint8_t*>(p.out[b]) + ((size_t)grow * p.ldo[b] + col0) * oes;
+            }
             store_row32(dst, v, nvalid, o32);
           }
+        }
+        if (use_tma) {
+          ptx::fence_proxy_async_shared();
+          __syncwarp();
+          if (lane == 0) {
+            ptx::tma_store_2d(tm_st, stg, ti.n0 + g * 64, st_row);
+            ptx::bulk_commit_group();
+          }
+          ++stg_count;
         }
       }
       // Release the accumulator to the MMA warp.
@@ -582,8 +637,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
 
-      if (p.mode == MODE_RS && !own) {
-        // Publish the tile to its owner: all 128 threads' stores, then one system-scope release.
+      if (rs_remote) {
+        // Publish the tile to its owner: every store of the four warps complete, then one
+        // system-scope release of the owner's flag for (this rank, this tile).
+        if (use_tma) {
+          if (lane == 0) ptx::bulk_wait_group<0>();
+        }
         __threadfence_system();
         ptx::named_bar_sync(2, EPI_WARPS * 32);
         if (epi_leader) {
@@ -591,6 +650,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
         }
       }
     }
+    if (lane == 0) ptx::bulk_wait_group<0>();   // shared memory must outlive the last stores
+    __syncwarp();
   } else {
     // ============================================================ communication warps (all-gather)
     if (p.mode == MODE_AG) {

@@ -258,7 +258,8 @@ def test_full_size_llama8b_mlp_properties(group):
     _freivalds(h1, A, w1, BF16_TOL)
     _freivalds(h3, A, w3, BF16_TOL)
     # column sums: 1^T C == (1^T A) B
-    torch.testing.assert_close(h1.double().sum(0), A.double().sum(0) @ w1.double(), rtol=1e-2, atol=0.5)
+    col_ref = A.double().sum(0) @ w1.double()
+    assert ((h1.double().sum(0) - col_ref).norm() / col_ref.norm()).item() <= BF16_TOL
     h = torch.nn.functional.silu(h1.float()).mul_(h3.float()).bfloat16()
     w2 = (torch.randn(1792, 4096, device="cuda") * 0.02).bfloat16()
     out = torch.ops._ap_symm_mem.fused_matmul_reduce_scatter(h, w2, "sum", 0, group)
@@ -355,7 +356,8 @@ def test_device_wait_times_out_cleanly(group):
     assert raw.value & 0xFF == 4 and raw.value >> 8 == 1  # peer partial, source rank 1
     assert b"peer partial" in L.apk_last_error()
     # the partial for the other rank was still produced, and the device still works
-    part = arena[: (M // 2) * N].view(M // 2, N)
+    # (epoch 1 uses the second half of the arena; slot 0 of it holds what rank 0 sent)
+    part = arena[M * N: M * N + (M // 2) * N].view(M // 2, N)
     assert orc.rel_fro_error(part, (A.double().cpu() @ B.double().cpu())[M // 2:]) <= BF16_TOL
     assert L.apk_check_status(C.byref(comm), stream, C.byref(raw)) == nat.APK_OK
     assert float((A.float() @ B.float()).sum()) == float((A.float() @ B.float()).sum())
