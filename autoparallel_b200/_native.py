@@ -48,6 +48,7 @@ EXPORTED_SYMBOLS = (
     "apk_ctrl_bytes",
     "apk_ag_gemm",
     "apk_gemm_rs",
+    "apk_ag_gemm_static",
     "apk_check_status",
     "apk_launch_count",
 )
@@ -156,6 +157,8 @@ def lib() -> C.CDLL:
     L.apk_ctrl_bytes.restype = C.c_uint64
     L.apk_ag_gemm.argtypes = [C.POINTER(ApkComm), C.POINTER(ApkAgGemmArgs), C.c_void_p]
     L.apk_gemm_rs.argtypes = [C.POINTER(ApkComm), C.POINTER(ApkGemmRsArgs), C.c_void_p]
+    L.apk_ag_gemm_static.argtypes = [C.POINTER(ApkComm), C.POINTER(ApkAgGemmArgs), C.c_void_p]
+    L.apk_ag_gemm_static.restype = C.c_int
     L.apk_check_status.argtypes = [C.POINTER(ApkComm), C.c_void_p, C.POINTER(C.c_uint32)]
     L.apk_launch_count.restype = C.c_uint64
     for name in ("apk_symm_alloc", "apk_symm_free", "apk_symm_export", "apk_symm_import", "apk_symm_unimport",

@@ -480,3 +480,71 @@ int apk_check_status(const apk_comm* comm, void* stream_, uint32_t* raw) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// apk_ag_gemm_static: the same all-gather matmul, with the library's own fixed scratch.
+//
+// Scratch that apk_ag_gemm expects from its caller (the per-call counters behind comm->ctrl, the
+// gathered copy of A when the caller does not want it back, the gathered row scales) lives here
+// in one file-scope device array instead. The array exists once per GPU that loads the library
+// and is shared by every call on that GPU.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr uint64_t kStaticCtrlBytes = 64ull << 10;       // per-call counters
+constexpr uint64_t kStaticScaleBytes = 256ull << 10;     // gathered row scales: up to 65536 rows
+constexpr uint64_t kStaticGatheredBytes = 32ull << 20;   // gathered A: world * rows_per_rank * K * element size
+constexpr uint64_t kStaticTotal = kStaticCtrlBytes + kStaticScaleBytes + kStaticGatheredBytes;
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticTotal];
+
+// Device address of g_static_scratch on the current device. In host code the array's name is
+// only a handle for the runtime, so the address is asked for once per device.
+int static_scratch_base(unsigned char** out) {
+  static unsigned char* base[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  APK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(APK_ERR_ARG, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lk(mu);
+  if (base[dev] == nullptr) {
+    void* p = nullptr;
+    APK_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    if (p == nullptr) return fail(APK_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    base[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = base[dev];
+  return APK_OK;
+}
+
+}  // namespace
+
+extern "C" int apk_ag_gemm_static(const apk_comm* comm, const apk_ag_gemm_args* a, void* stream_) {
+  if (comm == nullptr) return fail(APK_ERR_ARG, "comm is null");
+  if (a == nullptr) return fail(APK_ERR_ARG, "args is null");
+  if (a->rows_per_rank < 0 || a->K <= 0 || comm->world < 1 || comm->world > APK_MAX_WORLD)
+    return fail(APK_ERR_ARG, "bad shape or group size");
+  const uint64_t es = a->dtype == APK_BF16 ? 2 : 1;
+  const uint64_t rows = (uint64_t)a->rows_per_rank * (uint64_t)comm->world;
+  const uint64_t gathered = rows * (uint64_t)a->K * es;
+  const uint64_t ctrl = apk_ctrl_bytes(a->rows_per_rank, comm->world);
+  if (!a->return_A && comm->world > 1 && gathered > kStaticGatheredBytes)
+    return fail(APK_ERR_SIZE, "apk_ag_gemm_static: the gathered A needs %llu bytes, the fixed scratch holds %llu; use apk_ag_gemm",
+                (unsigned long long)gathered, (unsigned long long)kStaticGatheredBytes);
+  if (a->a_scale_mode == APK_SCALE_VECTOR && rows * 4 > kStaticScaleBytes)
+    return fail(APK_ERR_SIZE, "apk_ag_gemm_static: %llu gathered rows, the fixed scratch holds scales for %llu; use apk_ag_gemm",
+                (unsigned long long)rows, (unsigned long long)(kStaticScaleBytes / 4));
+  if (ctrl > kStaticCtrlBytes)
+    return fail(APK_ERR_SIZE, "apk_ag_gemm_static: %llu bytes of counters needed, the fixed scratch holds %llu; use apk_ag_gemm",
+                (unsigned long long)ctrl, (unsigned long long)kStaticCtrlBytes);
+  unsigned char* base = nullptr;
+  int rc = static_scratch_base(&base);
+  if (rc != APK_OK) return rc;
+  apk_comm c = *comm;
+  c.ctrl = base;                      // zeroed by apk_ag_gemm for the part each call uses
+  c.ctrl_bytes = kStaticCtrlBytes;
+  apk_ag_gemm_args args = *a;
+  args.A_scale_gathered = reinterpret_cast<float*>(base + kStaticCtrlBytes);
+  if (!a->return_A) args.A_gathered = base + kStaticCtrlBytes + kStaticScaleBytes;
+  return apk_ag_gemm(&c, &args, stream_);
+}

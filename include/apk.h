@@ -157,6 +157,27 @@ uint64_t apk_ctrl_bytes(int32_t rows_per_rank, int32_t world);
 int apk_ag_gemm(const apk_comm* comm, const apk_ag_gemm_args* args, void* stream);
 int apk_gemm_rs(const apk_comm* comm, const apk_gemm_rs_args* args, void* stream);
 
+/*
+ * apk_ag_gemm without caller-provided scratch. It has no counterpart in the reference.
+ *
+ * For callers that cannot allocate device memory around the op: a serving runtime that has
+ * already handed the whole GPU to its own pool (a cudaMalloc there fails or eats into the
+ * pool's headroom), or code on a path where allocating is forbidden because cudaMalloc may
+ * synchronise the device. Inputs and outputs are passed as for apk_ag_gemm; comm->status stays
+ * the caller's word, because the caller reads it. The scratch apk_ag_gemm takes from its caller
+ * is ignored and comes from one fixed device array inside the library instead:
+ *   comm->ctrl / ctrl_bytes   per-call counters, up to 64 KiB
+ *   args->A_gathered          only when return_A == 0: up to 32 MiB (world * rows_per_rank * K * element size)
+ *   args->A_scale_gathered    up to 65536 gathered rows
+ * A call that needs more returns APK_ERR_SIZE and launches nothing. The function calls no
+ * cudaMalloc / cudaFree. The first call on a device looks up the array's address and sets the
+ * kernel's shared-memory attribute, so make that first call outside any stream capture.
+ * Every call on a GPU uses the same array (it keeps the previous call's contents; the counters
+ * are cleared per call): calls that may overlap on the GPU, e.g. on two streams, race.
+ * Each GPU that loads the library holds the 32.3 MiB array until the process exits.
+ */
+int apk_ag_gemm_static(const apk_comm* comm, const apk_ag_gemm_args* args, void* stream);
+
 /* Synchronises `stream`, reads the status word, clears it; APK_ERR_TIMEOUT if it was set. */
 int apk_check_status(const apk_comm* comm, void* stream, uint32_t* raw);
 
