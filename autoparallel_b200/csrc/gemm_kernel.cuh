@@ -1,6 +1,6 @@
 // Persistent tcgen05/TMEM GEMM for sm_100a with the two async-TP fusions built in.
 //
-// One CTA per SM, 10 warps:
+// One CTA per SM, 14 warps:
 //   warp 0      TMA producer: waits for the rows of A it needs to be present in local
 //               memory (all-gather mode), then streams A/B tiles into a shared-memory ring.
 //   warp 1      MMA issuer: one thread issues tcgen05.mma into a double-buffered TMEM
@@ -9,7 +9,7 @@
 //               tiles owned by another rank are written straight into that rank's staging
 //               arena over NVLink and its per-tile flag is released; tiles owned by this rank
 //               are computed last and summed with the partials that arrived from the peers.
-//   warps 6-9   communication (all-gather mode): stage the local shard in the symmetric
+//   warps 6-13  communication (all-gather mode): stage the local shard in the symmetric
 //               buffer, tell the peers, then pull every peer's shard in ring order
 //               (rank+1, rank+2, ...) into the local gathered-A buffer in 4 KiB pieces,
 //               bumping a per-row-block counter the producer waits on.
@@ -36,7 +36,7 @@ constexpr int ROW_BYTES = 128;      // bytes per shared-memory row = TMA inner b
 constexpr int MAX_B = 4;            // weight matrices sharing one gathered A
 constexpr int MAX_WORLD = 8;
 constexpr int EPI_WARPS = 4;
-constexpr int COMM_WARPS = 4;
+constexpr int COMM_WARPS = 8;
 constexpr int NUM_THREADS = 32 * (2 + EPI_WARPS + COMM_WARPS);
 constexpr int PIECE_BYTES = 4096;   // unit of the all-gather pull: 32 lanes x 16 B x 8
 constexpr int FLAG_STRIDE = 32;     // u32 words between two ranks' "staged" flags (128 B)
@@ -486,6 +486,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
     const bool epi_leader = (warp == 2 && lane == 0);
     const uint32_t stg_base = smem_base + L::STG_OFF + (warp - 2) * L::STG_WARP_BYTES;
     uint32_t stg_count = 0;
+    // Reduce-scatter: a tile sent to its owner and not yet announced (same value in all 4 warps).
+    bool pub_pending = false, pub_generic = false;
+    uint32_t* pub_flag = nullptr;
+    auto publish_pending = [&]() {
+      if (!pub_pending) return;
+      // every store of the four warps complete (TMA: the issuing lanes' bulk groups; direct
+      // stores: each thread's own), then one system-scope release of the owner's flag
+      if (lane == 0) ptx::bulk_wait_group<0>();
+      if (pub_generic || lane == 0) __threadfence_system();
+      ptx::named_bar_sync(2, EPI_WARPS * 32);
+      if (epi_leader) ptx::st_release_sys(pub_flag, p.epoch);
+      pub_pending = false;
+    };
     uint32_t lt = 0;
     for (int t = blockIdx.x; t < sched.total_tiles; t += gridDim.x, ++lt) {
       const TileInfo ti = decode_tile<BN>(p, sched, t);
@@ -497,6 +510,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       const int b = ti.b;
       const bool own = (p.mode != MODE_RS) || (ti.chunk == p.rank);
 
+      // Before waiting on the peers, announce what this CTA still owes them: two ranks that each
+      // held back their last partial while waiting for the other's would wait forever.
+      if (p.mode == MODE_RS && own) publish_pending();
       // One thread does the waiting (peers' partials for a tile this rank owns, then the
       // accumulator); its verdict is shared so that all four warps leave the loop together.
       if (epi_leader) {
@@ -514,6 +530,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       ptx::named_bar_sync(1, EPI_WARPS * 32);
       if (epi_verdict[lt & 1u] == 0u) break;
       ptx::tc_fence_after();
+      publish_pending();
 
       // Row / tile constants of the scaled epilogue. Read only now: the gathered row scales of a
       // peer's chunk are in place once the accumulator that consumed those rows is complete.
@@ -638,18 +655,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
 
       if (rs_remote) {
-        // Publish the tile to its owner: every store of the four warps complete, then one
-        // system-scope release of the owner's flag for (this rank, this tile).
-        if (use_tma) {
-          if (lane == 0) ptx::bulk_wait_group<0>();
-        }
-        __threadfence_system();
-        ptx::named_bar_sync(2, EPI_WARPS * 32);
-        if (epi_leader) {
-          ptx::st_release_sys(p.rs_flag_peer[ti.chunk] + (size_t)p.rank * p.rs_max_tiles + ti.tile_in_chunk, p.epoch);
-        }
+        // The owner's flag for this tile is released at the start of the next tile (or after the
+        // loop), when the stores have had a whole mainloop to land on the peer.
+        pub_pending = true;
+        pub_generic = !use_tma;
+        pub_flag = p.rs_flag_peer[ti.chunk] + (size_t)p.rank * p.rs_max_tiles + ti.tile_in_chunk;
       }
     }
+    publish_pending();
     if (lane == 0) ptx::bulk_wait_group<0>();   // shared memory must outlive the last stores
     __syncwarp();
   } else {
@@ -718,6 +731,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
             if (lane == 0) ptx::red_add_release_gpu(ready + mt, 1u);
           }
         }
+        // Software pipeline: the loads of piece i are in flight while piece i-1 (stored in the
+        // previous iteration) is fenced and published, so a warp pays max(load, store-ack)
+        // latency per piece instead of their sum.
+        int prev_mt = -1;
         for (int q = gw; q < chunk_pieces; q += total_warps) {
           const int mt = q / full_pieces;
           const int j = q - mt * full_pieces;
@@ -725,11 +742,30 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
           const long long tile_end = min(tile_start + tile_bytes, (long long)p.ag_chunk_bytes);
           const long long off = tile_start + (long long)j * PIECE_BYTES;
           const int n16 = (int)(min((long long)PIECE_BYTES, tile_end - off) >> 4);
-          copy_piece<true>(peer + off, dst + off, nullptr, n16, lane);
+          uint4 r[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int i = u * 32 + lane;
+            if (i < n16) r[u] = ptx::ld_relaxed_sys_v4(peer + off + (size_t)i * 16);
+          }
+          if (prev_mt >= 0) {
+            ptx::fence_proxy_async_global();
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) ptx::red_add_release_gpu(ready + prev_mt, 1u);
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int i = u * 32 + lane;
+            if (i < n16) reinterpret_cast<uint4*>(dst + off)[i] = r[u];
+          }
+          prev_mt = mt;
+        }
+        if (prev_mt >= 0) {
           ptx::fence_proxy_async_global();
           __threadfence();
           __syncwarp();
-          if (lane == 0) ptx::red_add_release_gpu(ready + mt, 1u);
+          if (lane == 0) ptx::red_add_release_gpu(ready + prev_mt, 1u);
         }
       }
     }
