@@ -269,10 +269,16 @@ uint64_t apk_ag_gemm_arena_bytes(const apk_ag_gemm_args* a, int32_t world) {
 
 uint64_t apk_gemm_rs_arena_bytes(const apk_gemm_rs_args* a, int32_t world) {
   if (a == nullptr || world <= 1) return 0;
-  const uint64_t oes = a->B.out_dtype == APK_F32 ? 4 : 2;
-  // one slot per source rank, each padded to whole 128-row tiles
-  const uint64_t slot_rows = align_up((uint64_t)(a->M / world), apk::BM);
-  return align_up((uint64_t)world * slot_rows * (uint64_t)a->B.N * oes, 256);
+  const uint64_t rows = (uint64_t)(a->M / world);
+  const uint64_t mt = (rows + apk::BM - 1) / apk::BM;
+  if (a->B.out_dtype == APK_F32) {
+    // fp32 partials: row-major, one slot per source rank padded to whole 128-row tiles
+    return align_up((uint64_t)world * mt * apk::BM * (uint64_t)a->B.N * 4, 256);
+  }
+  // bf16 partials: whole tiles, stored as contiguous 32 x 64 blocks
+  const uint64_t bn = a->B.N <= 128 ? 128 : 256;
+  const uint64_t nt = ((uint64_t)a->B.N + bn - 1) / bn;
+  return (uint64_t)world * mt * nt * apk::BM * bn * 2;
 }
 
 uint64_t apk_ctrl_bytes(int32_t rows_per_rank, int32_t world) {
@@ -450,8 +456,7 @@ int apk_gemm_rs(const apk_comm* comm, const apk_gemm_rs_args* a, void* stream_) 
       kp.rs_arena_peer[r] = reinterpret_cast<uint8_t*>(comm->data[r]) + off;
       kp.rs_flag_peer[r] = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(comm->flags[r]) + kFlagRsOffset);
       if (a->B.out_dtype == APK_BF16 && r != comm->rank) {
-        rc = encode_2d(&kp.tmArena[r], APK_BF16, kp.rs_arena_peer[r], (uint64_t)a->B.N, (uint64_t)ws * kp.rs_slot_rows,
-                       (uint64_t)a->B.N, 64, 32, "peer arena");
+        rc = encode_2d(&kp.tmArena[r], APK_BF16, kp.rs_arena_peer[r], 64, need / 128, 64, 64, 32, "peer arena");
         if (rc != APK_OK) return rc;
       }
     }

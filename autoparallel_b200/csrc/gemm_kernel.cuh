@@ -57,7 +57,7 @@ struct alignas(64) KParams {
   CUtensorMap tmA1;            // AG: the gathered A [M, K]
   CUtensorMap tmB[MAX_B];
   CUtensorMap tmOut[MAX_B];            // bf16 outputs, box 32 rows x 64 columns (TMA stores)
-  CUtensorMap tmArena[MAX_WORLD];      // RS: every peer's arena half as [ws * rs_slot_rows, N]
+  CUtensorMap tmArena[MAX_WORLD];      // RS: every peer's arena half as [blocks * 32, 64] bf16 (blocked layout)
   int32_t mode, ws, rank, nB;
   int32_t M, K, rows_per_rank, elem_bytes;
   int32_t N[MAX_B];
@@ -91,7 +91,8 @@ struct alignas(64) KParams {
   uint32_t* ready;                     // [ws * tiles_m_per_chunk] local counters, zeroed per call
   uint32_t* ctrl;                      // local scratch counters, zeroed per call
   // ---- reduce-scatter
-  uint8_t* rs_arena_local;             // [ws][rs_slot_rows][N] partials (current parity)
+  uint8_t* rs_arena_local;             // partials (current parity): bf16 blocked [ws][tile][BN/64][4][32][64],
+                                       // fp32 row-major [ws][rs_slot_rows][N]
   uint8_t* rs_arena_peer[MAX_WORLD];
   uint32_t* rs_flag_local;             // [ws][rs_max_tiles]
   uint32_t* rs_flag_peer[MAX_WORLD];
@@ -153,21 +154,39 @@ __device__ __forceinline__ Sched make_sched(const KParams& p) {
   return s;
 }
 
+// Tile order. Rows of the local rank's chunk form one block of tiles_per_chunk tiles (first in
+// all-gather mode, last in reduce-scatter mode). The other ranks' chunks are interleaved row
+// block by row block: (row block 0 of rank+1, row block 0 of rank+2, ..., row block 1 of rank+1, ...),
+// so that at any moment a GPU exchanges data with all of its peers at once. On an NVSwitch
+// fabric this keeps every GPU's ingress and egress busy even when the ranks drift apart,
+// which a strict "one peer per step" order does not.
 template <int BN>
 __device__ __forceinline__ TileInfo decode_tile(const KParams& p, const Sched& s, int t) {
   TileInfo ti;
-  const int step = t / s.tiles_per_chunk;
-  int r = t - step * s.tiles_per_chunk;
-  if (p.mode == MODE_AG) {
-    ti.chunk = (p.rank + step) % p.ws;
-  } else if (p.mode == MODE_RS) {
-    ti.chunk = (p.rank + 1 + step) % p.ws;
+  int nt;
+  if (p.mode == MODE_PLAIN || p.ws == 1) {
+    ti.chunk = (p.mode == MODE_PLAIN) ? 0 : p.rank;
+    ti.mt = t / s.nt_total;
+    nt = t - ti.mt * s.nt_total;
   } else {
-    ti.chunk = 0;
+    const int remote_tiles = s.tiles_per_chunk * (p.ws - 1);
+    const bool own = (p.mode == MODE_AG) ? (t < s.tiles_per_chunk) : (t >= remote_tiles);
+    if (own) {
+      const int r = (p.mode == MODE_AG) ? t : t - remote_tiles;
+      ti.chunk = p.rank;
+      ti.mt = r / s.nt_total;
+      nt = r - ti.mt * s.nt_total;
+    } else {
+      const int r = (p.mode == MODE_AG) ? t - s.tiles_per_chunk : t;
+      const int per_mt = s.nt_total * (p.ws - 1);
+      ti.mt = r / per_mt;
+      const int rr = r - ti.mt * per_mt;
+      const int step = rr / s.nt_total;                 // 0 .. ws-2
+      nt = rr - step * s.nt_total;
+      ti.chunk = (p.rank + 1 + step) % p.ws;
+    }
   }
-  ti.mt = r / s.nt_total;
-  int nt = r - ti.mt * s.nt_total;
-  ti.tile_in_chunk = r;
+  ti.tile_in_chunk = ti.mt * s.nt_total + nt;
   ti.b = 0;
 #pragma unroll
   for (int b = 0; b < MAX_B - 1; ++b) {
@@ -556,14 +575,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       const int oes = o32 ? 4 : 2;
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
       const bool rs_remote = (p.mode == MODE_RS) && !own;
-      // Stores go through shared memory and TMA (full 128-byte rows, also over NVLink) whenever
-      // TMA's clipping is enough: bf16, and either all 128 rows exist or the rows past the end
-      // land in the padding of this rank's arena slot.
+      // Stores go through shared memory and TMA whenever TMA's clipping is enough: bf16, and either
+      // all 128 rows exist (local outputs) or the target is a peer's arena, which is laid out in
+      // whole 32 x 64 blocks so that every store over NVLink is one contiguous 4 KiB write
+      // (row-strided 128-byte writes reach a small fraction of the link rate).
       const bool use_tma = rs_remote ? (p.rs_arena_tma != 0) : (p.out_tma[b] != 0 && ti.rows_valid == BM);
       const CUtensorMap* tm_st = rs_remote ? &p.tmArena[ti.chunk] : &p.tmOut[b];
       int st_row;  // first row this warp stores, in the coordinates of tm_st
       if (rs_remote) {
-        st_row = p.rank * p.rs_slot_rows + ti.mt * BM + quarter * 32;
+        st_row = 0;  // computed per 64-column group below
       } else if (p.mode == MODE_RS) {
         st_row = ti.mt * BM + quarter * 32;
       } else {
@@ -608,8 +628,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
             if (row_ok) {
               for (int src = 0; src < p.ws; ++src) {
                 if (src == p.rank) continue;
-                const uint8_t* part = p.rs_arena_local +
-                                      (((size_t)src * p.rs_slot_rows + chunk_row) * p.N[b] + col0) * oes;
+                const uint8_t* part;
+                if (p.rs_arena_tma) {
+                  // blocked arena: one contiguous 4 KiB block per (source, tile, 64-column group, 32-row quarter)
+                  const size_t blk = ((((size_t)src * sched.tiles_per_chunk + ti.tile_in_chunk) * (BN / 64) + g) * 4 + quarter);
+                  part = p.rs_arena_local + (blk * 32 + lane) * ROW_BYTES + hf * 64;
+                } else {
+                  part = p.rs_arena_local + (((size_t)src * p.rs_slot_rows + chunk_row) * p.N[b] + col0) * oes;
+                }
                 add_row32(part, v, nvalid, o32);
               }
             }
@@ -643,7 +669,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
           ptx::fence_proxy_async_shared();
           __syncwarp();
           if (lane == 0) {
-            ptx::tma_store_2d(tm_st, stg, ti.n0 + g * 64, st_row);
+            if (rs_remote) {
+              // the peer's arena is addressed as [blocks * 32 rows][64 columns]: a contiguous 4 KiB write
+              const int blk = (((p.rank * sched.tiles_per_chunk + ti.tile_in_chunk) * (BN / 64) + g) * 4 + quarter);
+              ptx::tma_store_2d(tm_st, stg, 0, blk * 32);
+            } else {
+              ptx::tma_store_2d(tm_st, stg, ti.n0 + g * 64, st_row);
+            }
             ptx::bulk_commit_group();
           }
           ++stg_count;
@@ -702,24 +734,33 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
         }
         __syncwarp();
       }
-      // ---- steps 1..ws-1: pull rank+step's shard, row block by row block.
-      bool ok = true;
-      for (int step = 1; step < p.ws && ok; ++step) {
-        const int src = (p.rank + step) % p.ws;
-        if (lane == 0) {
-          ok = flag_wait<true>(p.staged_local + src * FLAG_STRIDE, p.epoch, p, abort_flag, ST_TIMEOUT_STAGED, (uint32_t)src);
-        }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) break;
-        const uint8_t* peer = p.ag_symm_peer[src];
-        uint8_t* dst = p.ag_gathered + (size_t)src * p.ag_chunk_bytes;
+      // ---- pull the peers' shards. Piece q of the schedule comes from peer rank+1+(q % (ws-1)), so
+      //      consecutive warps read from different peers and every row block of every peer fills
+      //      at the same pace (the order the tile schedule consumes them in).
+      if (p.ws > 1) {
+        const int npeers = p.ws - 1;
         const long long tile_bytes = (long long)BM * p.K * p.elem_bytes;
-        const int chunk_pieces = (sched.mt_per_chunk - 1) * full_pieces + ag_tile_pieces(p, sched.mt_per_chunk - 1);
-        uint32_t* ready = p.ready + src * sched.mt_per_chunk;
+        uint32_t seen = 0;   // peers whose "staged" flag this warp has acquired
+        bool ok = true;
+        auto acquire_peer = [&](int src) -> bool {
+          if (seen & (1u << src)) return true;
+          bool good = true;
+          if (lane == 0) {
+            good = flag_wait<true>(p.staged_local + src * FLAG_STRIDE, p.epoch, p, abort_flag, ST_TIMEOUT_STAGED, (uint32_t)src);
+          }
+          good = __shfl_sync(0xffffffffu, good ? 1 : 0, 0) != 0;
+          seen |= (1u << src);
+          return good;
+        };
         if (p.ag_has_scale) {
-          const float* ps = reinterpret_cast<const float*>(peer + p.ag_scale_off);
-          float* gs = p.ag_scale_gathered + (size_t)src * p.rows_per_rank;
-          for (int mt = gw; mt < sched.mt_per_chunk; mt += total_warps) {
+          const int units = sched.mt_per_chunk * npeers;
+          for (int v = gw; v < units && ok; v += total_warps) {
+            const int src = (p.rank + 1 + v % npeers) % p.ws;
+            const int mt = v / npeers;
+            ok = acquire_peer(src);
+            if (!ok) break;
+            const float* ps = reinterpret_cast<const float*>(p.ag_symm_peer[src] + p.ag_scale_off);
+            float* gs = p.ag_scale_gathered + (size_t)src * p.rows_per_rank;
             const int rows = min(BM, p.rows_per_rank - mt * BM);
             for (int i = lane; i < rows; i += 32) {
               uint32_t w;
@@ -728,19 +769,26 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
             }
             __threadfence();
             __syncwarp();
-            if (lane == 0) ptx::red_add_release_gpu(ready + mt, 1u);
+            if (lane == 0) ptx::red_add_release_gpu(p.ready + src * sched.mt_per_chunk + mt, 1u);
           }
         }
         // Software pipeline: the loads of piece i are in flight while piece i-1 (stored in the
-        // previous iteration) is fenced and published, so a warp pays max(load, store-ack)
-        // latency per piece instead of their sum.
-        int prev_mt = -1;
-        for (int q = gw; q < chunk_pieces; q += total_warps) {
-          const int mt = q / full_pieces;
-          const int j = q - mt * full_pieces;
+        // previous iteration) is fenced and published.
+        const long long total_q = (long long)sched.mt_per_chunk * full_pieces * npeers;
+        uint32_t* prev_ready = nullptr;
+        for (long long q = gw; q < total_q && ok; q += total_warps) {
+          const int src = (p.rank + 1 + (int)(q % npeers)) % p.ws;
+          const long long qq = q / npeers;
+          const int mt = (int)(qq / full_pieces);
+          const int j = (int)(qq - (long long)mt * full_pieces);
           const long long tile_start = (long long)mt * tile_bytes;
           const long long tile_end = min(tile_start + tile_bytes, (long long)p.ag_chunk_bytes);
           const long long off = tile_start + (long long)j * PIECE_BYTES;
+          if (off >= tile_end) continue;   // the last row block of a chunk may have fewer pieces
+          ok = acquire_peer(src);
+          if (!ok) break;
+          const uint8_t* peer = p.ag_symm_peer[src];
+          uint8_t* dst = p.ag_gathered + (size_t)src * p.ag_chunk_bytes;
           const int n16 = (int)(min((long long)PIECE_BYTES, tile_end - off) >> 4);
           uint4 r[8];
 #pragma unroll
@@ -748,24 +796,24 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
             const int i = u * 32 + lane;
             if (i < n16) r[u] = ptx::ld_relaxed_sys_v4(peer + off + (size_t)i * 16);
           }
-          if (prev_mt >= 0) {
+          if (prev_ready != nullptr) {
             ptx::fence_proxy_async_global();
             __threadfence();
             __syncwarp();
-            if (lane == 0) ptx::red_add_release_gpu(ready + prev_mt, 1u);
+            if (lane == 0) ptx::red_add_release_gpu(prev_ready, 1u);
           }
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
             const int i = u * 32 + lane;
             if (i < n16) reinterpret_cast<uint4*>(dst + off)[i] = r[u];
           }
-          prev_mt = mt;
+          prev_ready = p.ready + src * sched.mt_per_chunk + mt;
         }
-        if (prev_mt >= 0) {
+        if (prev_ready != nullptr) {
           ptx::fence_proxy_async_global();
           __threadfence();
           __syncwarp();
-          if (lane == 0) ptx::red_add_release_gpu(ready + prev_mt, 1u);
+          if (lane == 0) ptx::red_add_release_gpu(prev_ready, 1u);
         }
       }
     }

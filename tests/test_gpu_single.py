@@ -320,6 +320,76 @@ def test_c_abi_direct_call_and_alignment_error(group):
     assert b"16-byte aligned" in L.apk_last_error()
 
 
+def _to_blocked(part, BN):
+    """[rows, N] bf16 partial -> the arena's layout for one source rank: per 128 x BN tile (row block
+    major), per 64-column group, per 32-row quarter, a contiguous [32, 64] block."""
+    rows, N = part.shape
+    mt, nt = (rows + 127) // 128, (N + BN - 1) // BN
+    pad = torch.zeros(mt * 128, nt * BN, dtype=part.dtype, device=part.device)
+    pad[:rows, :N] = part
+    return pad.view(mt, 4, 32, nt, BN // 64, 64).permute(0, 3, 4, 1, 2, 5).contiguous().view(-1)
+
+
+@pytest.mark.parametrize("world,M,K,N", [(2, 512, 256, 256), (4, 4 * 384, 192, 328), (8, 8 * 128, 128, 64)])
+def test_reduce_scatter_receive_side_on_one_gpu(group, world, M, K, N):
+    """Rank 0 of a `world`-rank reduce-scatter on a single GPU: the peers' partials for rank 0's rows
+    are placed in its arena beforehand and their tile flags are set, so the epilogue's wait, its
+    read of the blocked arena and the fp32 sum run exactly as with live peers. What rank 0 sends
+    to the others lands in scratch arenas and is checked too."""
+    from autoparallel_b200 import _native as nat
+
+    L = nat.lib()
+    orc = _orc()
+    rows = M // world
+    BN = 128 if N <= 128 else 256
+    A = orc.activations(0, M, K)
+    B = orc.weights(7, K, N)
+    peers = [orc.activations(10 + r, rows, N) * 0.3 for r in range(world)]   # bf16 partials of ranks 1..world-1
+    args0 = nat.ApkGemmRsArgs()
+    args0.M, args0.B.N, args0.B.out_dtype = M, N, nat.APK_BF16
+    half = int(L.apk_gemm_rs_arena_bytes(C.byref(args0), world))
+    slot = half // world
+    arenas = [torch.zeros(2 * half, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    for h in range(2):
+        for src in range(1, world):
+            blk = _to_blocked(peers[src].cuda(), BN).view(torch.uint8)
+            arenas[0][h * half + src * slot: h * half + src * slot + blk.numel()] = blk
+    pads = [torch.zeros(1 << 17, dtype=torch.int32, device="cuda") for _ in range(world)]
+    pads[0][1024:] = 1000      # every (source, tile) flag of rank 0 is already raised (tile flags start at byte 4096)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ctrl = torch.zeros(1024, dtype=torch.int32, device="cuda")
+    Ad, Bd = A.cuda(), B.cuda()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    full64 = A.double() @ B.double()
+    for epoch in (1, 2):
+        out = torch.full((rows, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        comm = nat.ApkComm()
+        comm.rank, comm.world = 0, world
+        for r in range(world):
+            comm.data[r], comm.flags[r] = arenas[r].data_ptr(), pads[r].data_ptr()
+        comm.data_bytes, comm.flag_bytes = 2 * half, pads[0].numel() * 4
+        comm.ctrl, comm.ctrl_bytes = ctrl.data_ptr(), ctrl.numel() * 4
+        comm.status, comm.epoch, comm.timeout_s = status.data_ptr(), epoch, 5.0
+        args = nat.ApkGemmRsArgs()
+        args.dtype, args.M, args.K, args.reduce_op = nat.APK_BF16, M, K, nat.APK_REDUCE_AVG
+        args.A, args.lda = Ad.data_ptr(), K
+        args.B.B, args.B.ldb, args.B.n_major, args.B.N = Bd.data_ptr(), N, 1, N
+        args.B.out, args.B.ldo, args.B.out_dtype = out.data_ptr(), N, nat.APK_BF16
+        assert L.apk_gemm_rs(C.byref(comm), C.byref(args), stream) == nat.APK_OK, L.apk_last_error()
+        raw = C.c_uint32(0)
+        assert L.apk_check_status(C.byref(comm), stream, C.byref(raw)) == nat.APK_OK, L.apk_last_error()
+        ref64 = (full64[:rows] + sum(peers[s].double() for s in range(1, world))) / world
+        assert orc.rel_fro_error(out, ref64) <= BF16_TOL
+        # what went out: peer d's arena, slot 0, holds rows [d*rows, (d+1)*rows) of A @ B in blocked form
+        off = (epoch & 1) * half
+        for d in range(1, world):
+            want = _to_blocked(full64[d * rows:(d + 1) * rows].to(torch.bfloat16).cuda(), BN)
+            got = arenas[d][off: off + want.numel() * 2].view(torch.bfloat16)
+            mask = want != 0   # padding columns / rows of a block are not specified
+            assert orc.rel_fro_error(got[mask].float(), want[mask].double().cpu()) <= BF16_TOL
+            assert int(pads[d][1024 + 0]) == epoch   # flag (source 0, tile 0) released with the epoch
+
+
 def test_device_wait_times_out_cleanly(group):
     """A two-rank reduce-scatter whose 'peer' is this GPU's own memory and never answers: the
     wait for the peer's partial runs out after timeout_s, the kernel frees its resources and
@@ -332,7 +402,7 @@ def test_device_wait_times_out_cleanly(group):
     A = orc.activations(0, M, K).cuda()
     B = orc.weights(7, K, N).cuda()
     out = torch.empty(M // 2, N, dtype=torch.bfloat16, device="cuda")
-    arena = torch.zeros(2 * M * N, dtype=torch.bfloat16, device="cuda")
+    arena = torch.zeros(2 * 2 * 128 * 128, dtype=torch.bfloat16, device="cuda")  # two halves of [2 ranks][1 tile of 128x128]
     flags = torch.zeros(8192 * 2, dtype=torch.int32, device="cuda")
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
     ctrl = torch.zeros(1024, dtype=torch.int32, device="cuda")
@@ -356,8 +426,10 @@ def test_device_wait_times_out_cleanly(group):
     assert raw.value & 0xFF == 4 and raw.value >> 8 == 1  # peer partial, source rank 1
     assert b"peer partial" in L.apk_last_error()
     # the partial for the other rank was still produced, and the device still works
-    # (epoch 1 uses the second half of the arena; slot 0 of it holds what rank 0 sent)
-    part = arena[M * N: M * N + (M // 2) * N].view(M // 2, N)
+    # (epoch 1 uses the second half of the arena; its first tile holds what rank 0 sent, stored as
+    #  32-row x 64-column blocks, which for N = 64 is plain row-major)
+    half = arena.numel() // 2
+    part = arena[half: half + (M // 2) * N].view(M // 2, N)
     assert orc.rel_fro_error(part, (A.double().cpu() @ B.double().cpu())[M // 2:]) <= BF16_TOL
     assert L.apk_check_status(C.byref(comm), stream, C.byref(raw)) == nat.APK_OK
     assert float((A.float() @ B.float()).sum()) == float((A.float() @ B.float()).sum())
