@@ -455,10 +455,6 @@ int apk_gemm_rs(const apk_comm* comm, const apk_gemm_rs_args* a, void* stream_) 
     for (int r = 0; r < ws; ++r) {
       kp.rs_arena_peer[r] = reinterpret_cast<uint8_t*>(comm->data[r]) + off;
       kp.rs_flag_peer[r] = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(comm->flags[r]) + kFlagRsOffset);
-      if (a->B.out_dtype == APK_BF16 && r != comm->rank) {
-        rc = encode_2d(&kp.tmArena[r], APK_BF16, kp.rs_arena_peer[r], 64, need / 128, 64, 64, 32, "peer arena");
-        if (rc != APK_OK) return rc;
-      }
     }
     kp.rs_arena_tma = a->B.out_dtype == APK_BF16;
     kp.rs_arena_local = kp.rs_arena_peer[comm->rank];

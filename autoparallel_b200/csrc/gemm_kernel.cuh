@@ -1,6 +1,6 @@
 // Persistent tcgen05/TMEM GEMM for sm_100a with the two async-TP fusions built in.
 //
-// One CTA per SM, 14 warps:
+// One CTA per SM, 12 warps:
 //   warp 0      TMA producer: waits for the rows of A it needs to be present in local
 //               memory (all-gather mode), then streams A/B tiles into a shared-memory ring.
 //   warp 1      MMA issuer: one thread issues tcgen05.mma into a double-buffered TMEM
@@ -9,7 +9,7 @@
 //               tiles owned by another rank are written straight into that rank's staging
 //               arena over NVLink and its per-tile flag is released; tiles owned by this rank
 //               are computed last and summed with the partials that arrived from the peers.
-//   warps 6-13  communication (all-gather mode): stage the local shard in the symmetric
+//   warps 6-11  communication (all-gather mode): stage the local shard in the symmetric
 //               buffer, tell the peers, then pull every peer's shard in ring order
 //               (rank+1, rank+2, ...) into the local gathered-A buffer in 4 KiB pieces,
 //               bumping a per-row-block counter the producer waits on.
@@ -36,7 +36,7 @@ constexpr int ROW_BYTES = 128;      // bytes per shared-memory row = TMA inner b
 constexpr int MAX_B = 4;            // weight matrices sharing one gathered A
 constexpr int MAX_WORLD = 8;
 constexpr int EPI_WARPS = 4;
-constexpr int COMM_WARPS = 8;
+constexpr int COMM_WARPS = 6;
 constexpr int NUM_THREADS = 32 * (2 + EPI_WARPS + COMM_WARPS);
 constexpr int PIECE_BYTES = 4096;   // unit of the all-gather pull: 32 lanes x 16 B x 8
 constexpr int FLAG_STRIDE = 32;     // u32 words between two ranks' "staged" flags (128 B)
@@ -57,7 +57,6 @@ struct alignas(64) KParams {
   CUtensorMap tmA1;            // AG: the gathered A [M, K]
   CUtensorMap tmB[MAX_B];
   CUtensorMap tmOut[MAX_B];            // bf16 outputs, box 32 rows x 64 columns (TMA stores)
-  CUtensorMap tmArena[MAX_WORLD];      // RS: every peer's arena half as [blocks * 32, 64] bf16 (blocked layout)
   int32_t mode, ws, rank, nB;
   int32_t M, K, rows_per_rank, elem_bytes;
   int32_t N[MAX_B];
@@ -98,7 +97,7 @@ struct alignas(64) KParams {
   uint32_t* rs_flag_peer[MAX_WORLD];
   int32_t rs_max_tiles;
   int32_t rs_slot_rows;                // rows_per_rank rounded up to whole 128-row tiles
-  int32_t rs_arena_tma;                // tmArena[] are valid
+  int32_t rs_arena_tma;                // bf16 partials: blocked arena written by bulk copies
   float reduce_scale;                  // 1 for sum, 1/ws for avg
   // ---- common
   uint32_t epoch;
@@ -315,6 +314,24 @@ __device__ __forceinline__ void add_row32(const void* src, float (&v)[32], int n
   }
 }
 
+// v += 32 bf16 values (half `hf` of a 64-column row) of a partial stored in the arena's blocked,
+// swizzled layout: 16-byte chunk c of row r sits at chunk position c ^ (r & 7).
+__device__ __forceinline__ void add_row32_swizzled(const uint8_t* row, int hf, int lane, float (&v)[32], int nvalid) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (j * 8 < nvalid) {
+      const uint32_t chunk = (uint32_t)(hf * 4 + j) ^ (uint32_t)(lane & 7);
+      const uint4 q = __ldcg(reinterpret_cast<const uint4*>(row + chunk * 16));
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        v[8 * j + 2 * e] += __uint_as_float(w[e] << 16);
+        v[8 * j + 2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+      }
+    }
+  }
+}
+
 // One warp copies up to 4 KiB (n16 16-byte words) src -> dst (and dst2 when given).
 template <bool PEER>
 __device__ __forceinline__ void copy_piece(const uint8_t* src, uint8_t* dst, uint8_t* dst2, int n16, int lane) {
@@ -505,18 +522,50 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
     const bool epi_leader = (warp == 2 && lane == 0);
     const uint32_t stg_base = smem_base + L::STG_OFF + (warp - 2) * L::STG_WARP_BYTES;
     uint32_t stg_count = 0;
-    // Reduce-scatter: a tile sent to its owner and not yet announced (same value in all 4 warps).
-    bool pub_pending = false, pub_generic = false;
-    uint32_t* pub_flag = nullptr;
-    auto publish_pending = [&]() {
-      if (!pub_pending) return;
-      // every store of the four warps complete (TMA: the issuing lanes' bulk groups; direct
-      // stores: each thread's own), then one system-scope release of the owner's flag
-      if (lane == 0) ptx::bulk_wait_group<0>();
-      if (pub_generic || lane == 0) __threadfence_system();
+    // Reduce-scatter: tiles sent to their owners and not yet announced, oldest first (the same
+    // values in all 4 warps). Up to four tiles stay in flight and flags are released two tiles at
+    // a time behind ONE system-scope fence: a fence costs a round trip over a busy NVLink, so it
+    // must neither be paid per tile nor wait for the newest stores.
+    uint32_t* pq_flag[4] = {nullptr, nullptr, nullptr, nullptr};
+    int pq_newer[4] = {0, 0, 0, 0};   // bulk groups this warp committed after the tile's own
+    bool pq_gen[4] = {false, false, false, false};
+    int pq_n = 0;
+    auto publish_oldest = [&](int count) {   // count = 1 or 2, count <= pq_n
+      // every store of the four warps for these tiles complete (bulk copies: the issuing lanes'
+      // groups; direct stores: each thread's own, fenced by itself), then the flags
+      const int newer = pq_newer[count - 1];
+      bool generic = pq_gen[0] || (count == 2 && pq_gen[1]);
+      if (lane == 0) ptx::bulk_wait_group_upto(newer);
+      if (generic) __threadfence_system();
       ptx::named_bar_sync(2, EPI_WARPS * 32);
-      if (epi_leader) ptx::st_release_sys(pub_flag, p.epoch);
-      pub_pending = false;
+      if (epi_leader) {
+        __threadfence_system();
+        ptx::st_relaxed_sys(pq_flag[0], p.epoch);
+        if (count == 2) ptx::st_relaxed_sys(pq_flag[1], p.epoch);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int j = i + count;
+        pq_flag[i] = (j < 4) ? pq_flag[j < 4 ? j : 3] : nullptr;
+        pq_newer[i] = (j < 4) ? pq_newer[j < 4 ? j : 3] : 0;
+        pq_gen[i] = (j < 4) ? pq_gen[j < 4 ? j : 3] : false;
+      }
+      pq_n -= count;
+    };
+    auto publish_pending = [&]() {
+      while (pq_n > 0) publish_oldest(pq_n >= 2 ? 2 : 1);
+    };
+    auto note_commit = [&]() {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) ++pq_newer[i];   // entries beyond pq_n are reset when they are filled
+    };
+    auto push_pending = [&](uint32_t* flag, bool generic) {
+      if (pq_n == 4) publish_oldest(2);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (i == pq_n) { pq_flag[i] = flag; pq_newer[i] = 0; pq_gen[i] = generic; }
+      }
+      ++pq_n;
     };
     uint32_t lt = 0;
     for (int t = blockIdx.x; t < sched.total_tiles; t += gridDim.x, ++lt) {
@@ -549,7 +598,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       ptx::named_bar_sync(1, EPI_WARPS * 32);
       if (epi_verdict[lt & 1u] == 0u) break;
       ptx::tc_fence_after();
-      publish_pending();
 
       // Row / tile constants of the scaled epilogue. Read only now: the gathered row scales of a
       // peer's chunk are in place once the accumulator that consumed those rows is complete.
@@ -575,12 +623,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       const int oes = o32 ? 4 : 2;
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
       const bool rs_remote = (p.mode == MODE_RS) && !own;
-      // Stores go through shared memory and TMA whenever TMA's clipping is enough: bf16, and either
-      // all 128 rows exist (local outputs) or the target is a peer's arena, which is laid out in
-      // whole 32 x 64 blocks so that every store over NVLink is one contiguous 4 KiB write
-      // (row-strided 128-byte writes reach a small fraction of the link rate).
+      // Stores go through shared memory and the TMA engine whenever that is possible: bf16, and
+      // either all 128 rows exist (local outputs, tiled store clipped at N) or the target is a
+      // peer's arena, which is laid out in whole 32 x 64 blocks so that every store over NVLink is
+      // one linear 4 KiB bulk copy (row-strided 128-byte writes reach a fraction of the link rate).
       const bool use_tma = rs_remote ? (p.rs_arena_tma != 0) : (p.out_tma[b] != 0 && ti.rows_valid == BM);
-      const CUtensorMap* tm_st = rs_remote ? &p.tmArena[ti.chunk] : &p.tmOut[b];
+      const CUtensorMap* tm_st = &p.tmOut[b];
       int st_row;  // first row this warp stores, in the coordinates of tm_st
       if (rs_remote) {
         st_row = 0;  // computed per 64-column group below
@@ -611,32 +659,56 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
           const int col0 = ti.n0 + c * 32;
           const int nvalid = min(32, p.N[b] - col0);
           if (scaled) {
+            // per-column operands are the same for every row (broadcast loads); 8 columns at a time
+            const bool full = (nvalid == 32);
+            const bool bs_vec = (bs_mode == 2) && full && ((reinterpret_cast<uintptr_t>(bs + col0) & 15u) == 0);
+            const bool bias_bf16 = (bias != nullptr) && !p.bias_fp32[b];
+            const __nv_bfloat16* bias_h = reinterpret_cast<const __nv_bfloat16*>(bias) + col0;
+            const float* bias_f = reinterpret_cast<const float*>(bias) + col0;
+            const bool bias_vec = bias_bf16 && full && ((reinterpret_cast<uintptr_t>(bias_h) & 15u) == 0);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float x = v[j] * sa;
-              if (j < nvalid) {
-                if (bs_mode == 2) x *= __ldg(bs + col0 + j);
-                if (bias != nullptr) {
-                  x += p.bias_fp32[b] ? __ldg(reinterpret_cast<const float*>(bias) + col0 + j)
-                                      : __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(bias) + col0 + j));
+            for (int j8 = 0; j8 < 4; ++j8) {
+              float cs[8], cb[8];
+              if (bs_vec) {
+                const float4 q0 = __ldg(reinterpret_cast<const float4*>(bs + col0) + 2 * j8);
+                const float4 q1 = __ldg(reinterpret_cast<const float4*>(bs + col0) + 2 * j8 + 1);
+                cs[0] = q0.x; cs[1] = q0.y; cs[2] = q0.z; cs[3] = q0.w; cs[4] = q1.x; cs[5] = q1.y; cs[6] = q1.z; cs[7] = q1.w;
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) cs[e] = (bs_mode == 2 && 8 * j8 + e < nvalid) ? __ldg(bs + col0 + 8 * j8 + e) : 1.0f;
+              }
+              if (bias_vec) {
+                const uint4 q = __ldg(reinterpret_cast<const uint4*>(bias_h) + j8);
+                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  cb[2 * e] = __uint_as_float(w[e] << 16);
+                  cb[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+                }
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const int j = 8 * j8 + e;
+                  cb[e] = (bias == nullptr || j >= nvalid) ? 0.0f : (bias_bf16 ? __bfloat162float(__ldg(bias_h + j)) : __ldg(bias_f + j));
                 }
               }
-              v[j] = x * rscale;
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[8 * j8 + e] = (v[8 * j8 + e] * sa * cs[e] + cb[e]) * rscale;
             }
           }
           if (p.mode == MODE_RS && own) {
             if (row_ok) {
               for (int src = 0; src < p.ws; ++src) {
                 if (src == p.rank) continue;
-                const uint8_t* part;
                 if (p.rs_arena_tma) {
-                  // blocked arena: one contiguous 4 KiB block per (source, tile, 64-column group, 32-row quarter)
+                  // blocked arena: one contiguous 4 KiB block per (source, tile, 64-column group,
+                  // 32-row quarter), rows of 128 bytes with their 16-byte chunks XOR-swizzled by row
                   const size_t blk = ((((size_t)src * sched.tiles_per_chunk + ti.tile_in_chunk) * (BN / 64) + g) * 4 + quarter);
-                  part = p.rs_arena_local + (blk * 32 + lane) * ROW_BYTES + hf * 64;
+                  add_row32_swizzled(p.rs_arena_local + (blk * 32 + lane) * ROW_BYTES, hf, lane, v, nvalid);
                 } else {
-                  part = p.rs_arena_local + (((size_t)src * p.rs_slot_rows + chunk_row) * p.N[b] + col0) * oes;
+                  const uint8_t* part = p.rs_arena_local + (((size_t)src * p.rs_slot_rows + chunk_row) * p.N[b] + col0) * oes;
+                  add_row32(part, v, nvalid, o32);
                 }
-                add_row32(part, v, nvalid, o32);
               }
             }
             if (p.reduce_scale != 1.0f) {
@@ -670,14 +742,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
           __syncwarp();
           if (lane == 0) {
             if (rs_remote) {
-              // the peer's arena is addressed as [blocks * 32 rows][64 columns]: a contiguous 4 KiB write
-              const int blk = (((p.rank * sched.tiles_per_chunk + ti.tile_in_chunk) * (BN / 64) + g) * 4 + quarter);
-              ptx::tma_store_2d(tm_st, stg, 0, blk * 32);
+              // one linear 4 KiB bulk copy of the staging buffer as it is (swizzled) into this
+              // tile's block of the peer's arena; the owner undoes the swizzle when it reads
+              const size_t blk = ((((size_t)p.rank * sched.tiles_per_chunk + ti.tile_in_chunk) * (BN / 64) + g) * 4 + quarter);
+              ptx::bulk_store(p.rs_arena_peer[ti.chunk] + blk * (32 * ROW_BYTES), stg, 32 * ROW_BYTES);
             } else {
               ptx::tma_store_2d(tm_st, stg, ti.n0 + g * 64, st_row);
             }
             ptx::bulk_commit_group();
           }
+          note_commit();
           ++stg_count;
         }
       }
@@ -687,11 +761,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
 
       if (rs_remote) {
-        // The owner's flag for this tile is released at the start of the next tile (or after the
-        // loop), when the stores have had a whole mainloop to land on the peer.
-        pub_pending = true;
-        pub_generic = !use_tma;
-        pub_flag = p.rs_flag_peer[ti.chunk] + (size_t)p.rank * p.rs_max_tiles + ti.tile_in_chunk;
+        // The owner's flag for this tile is released once three newer tiles are queued behind it,
+        // before this CTA waits on its peers, or after the loop.
+        push_pending(p.rs_flag_peer[ti.chunk] + (size_t)p.rank * p.rs_max_tiles + ti.tile_in_chunk, !use_tma);
       }
     }
     publish_pending();

@@ -59,6 +59,10 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int
                ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(x), "r"(y)
                : "memory");
 }
+// Linear (untiled) bulk copy shared -> global; addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
@@ -71,6 +75,24 @@ __device__ __forceinline__ void bulk_wait_group_read() {
 template <int N>
 __device__ __forceinline__ void bulk_wait_group() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+// Same with a run-time bound (0..12); larger values wait for everything.
+__device__ __forceinline__ void bulk_wait_group_upto(int n) {
+  switch (n) {
+    case 9: bulk_wait_group<9>(); break;
+    case 10: bulk_wait_group<10>(); break;
+    case 11: bulk_wait_group<11>(); break;
+    case 12: bulk_wait_group<12>(); break;
+    case 1: bulk_wait_group<1>(); break;
+    case 2: bulk_wait_group<2>(); break;
+    case 3: bulk_wait_group<3>(); break;
+    case 4: bulk_wait_group<4>(); break;
+    case 5: bulk_wait_group<5>(); break;
+    case 6: bulk_wait_group<6>(); break;
+    case 7: bulk_wait_group<7>(); break;
+    case 8: bulk_wait_group<8>(); break;
+    default: bulk_wait_group<0>(); break;
+  }
 }
 // Orders generic-proxy shared-memory writes before async-proxy (TMA) reads of them.
 __device__ __forceinline__ void fence_proxy_async_shared() {
@@ -148,6 +170,9 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
 }
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ void red_add_release_gpu(uint32_t* p, uint32_t v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");

@@ -327,7 +327,10 @@ def _to_blocked(part, BN):
     mt, nt = (rows + 127) // 128, (N + BN - 1) // BN
     pad = torch.zeros(mt * 128, nt * BN, dtype=part.dtype, device=part.device)
     pad[:rows, :N] = part
-    return pad.view(mt, 4, 32, nt, BN // 64, 64).permute(0, 3, 4, 1, 2, 5).contiguous().view(-1)
+    blocks = pad.view(mt, 4, 32, nt, BN // 64, 64).permute(0, 3, 4, 1, 2, 5).contiguous().view(-1, 32, 8, 8)
+    pos = torch.arange(8, device=part.device)[None, :] ^ (torch.arange(32, device=part.device) % 8)[:, None]
+    idx = pos[None, :, :, None].expand(blocks.shape[0], 32, 8, 8)
+    return blocks.gather(2, idx).contiguous().view(-1)
 
 
 @pytest.mark.parametrize("world,M,K,N", [(2, 512, 256, 256), (4, 4 * 384, 192, 328), (8, 8 * 128, 128, 64)])
@@ -426,10 +429,12 @@ def test_device_wait_times_out_cleanly(group):
     assert raw.value & 0xFF == 4 and raw.value >> 8 == 1  # peer partial, source rank 1
     assert b"peer partial" in L.apk_last_error()
     # the partial for the other rank was still produced, and the device still works
-    # (epoch 1 uses the second half of the arena; its first tile holds what rank 0 sent, stored as
-    #  32-row x 64-column blocks, which for N = 64 is plain row-major)
+    # (epoch 1 uses the second half of the arena; its first tile holds what rank 0 sent, in the
+    #  arena's blocked layout)
     half = arena.numel() // 2
-    part = arena[half: half + (M // 2) * N].view(M // 2, N)
-    assert orc.rel_fro_error(part, (A.double().cpu() @ B.double().cpu())[M // 2:]) <= BF16_TOL
+    want = _to_blocked((A.double().cpu() @ B.double().cpu())[M // 2:].to(torch.bfloat16).cuda(), 128)
+    got = arena[half: half + want.numel()]
+    mask = want != 0
+    assert orc.rel_fro_error(got[mask].float(), want[mask].double().cpu()) <= BF16_TOL
     assert L.apk_check_status(C.byref(comm), stream, C.byref(raw)) == nat.APK_OK
     assert float((A.float() @ B.float()).sum()) == float((A.float() @ B.float()).sum())
