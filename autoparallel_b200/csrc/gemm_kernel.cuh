@@ -314,24 +314,6 @@ __device__ __forceinline__ void add_row32(const void* src, float (&v)[32], int n
   }
 }
 
-// v += 32 bf16 values (half `hf` of a 64-column row) of a partial stored in the arena's blocked,
-// swizzled layout: 16-byte chunk c of row r sits at chunk position c ^ (r & 7).
-__device__ __forceinline__ void add_row32_swizzled(const uint8_t* row, int hf, int lane, float (&v)[32], int nvalid) {
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    if (j * 8 < nvalid) {
-      const uint32_t chunk = (uint32_t)(hf * 4 + j) ^ (uint32_t)(lane & 7);
-      const uint4 q = __ldcg(reinterpret_cast<const uint4*>(row + chunk * 16));
-      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        v[8 * j + 2 * e] += __uint_as_float(w[e] << 16);
-        v[8 * j + 2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
-      }
-    }
-  }
-}
-
 // One warp copies up to 4 KiB (n16 16-byte words) src -> dst (and dst2 when given).
 template <bool PEER>
 __device__ __forceinline__ void copy_piece(const uint8_t* src, uint8_t* dst, uint8_t* dst2, int n16, int lane) {
@@ -697,18 +679,48 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
             }
           }
           if (p.mode == MODE_RS && own) {
-            if (row_ok) {
+            if (row_ok && p.rs_arena_tma) {
+              // Blocked arena: one contiguous 4 KiB block per (source, tile, 64-column group, 32-row
+              // quarter), rows of 128 bytes whose 16-byte chunks are XOR-swizzled by row. The loads
+              // of four sources are issued before any of them is consumed: a thread that waited for
+              // one source at a time would pay a memory latency per source.
+              const size_t blk0 = (((size_t)ti.tile_in_chunk * (BN / 64) + g) * 4 + quarter) * 32 + lane;
+              const size_t src_stride = (size_t)sched.tiles_per_chunk * (BN / 64) * 4 * 32;
+              for (int s0 = 0; s0 < p.ws; s0 += 4) {
+                uint4 q[4][4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  const int src = s0 + u;
+                  if (src < p.ws && src != p.rank) {
+                    const uint8_t* row = p.rs_arena_local + (blk0 + (size_t)src * src_stride) * ROW_BYTES;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                      const uint32_t chunk = (uint32_t)(hf * 4 + j) ^ (uint32_t)(lane & 7);
+                      q[u][j] = (j * 8 < nvalid) ? __ldcg(reinterpret_cast<const uint4*>(row + chunk * 16)) : make_uint4(0, 0, 0, 0);
+                    }
+                  }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  const int src = s0 + u;
+                  if (src < p.ws && src != p.rank) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                      const uint32_t w[4] = {q[u][j].x, q[u][j].y, q[u][j].z, q[u][j].w};
+#pragma unroll
+                      for (int e = 0; e < 4; ++e) {
+                        v[8 * j + 2 * e] += __uint_as_float(w[e] << 16);
+                        v[8 * j + 2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+                      }
+                    }
+                  }
+                }
+              }
+            } else if (row_ok) {
               for (int src = 0; src < p.ws; ++src) {
                 if (src == p.rank) continue;
-                if (p.rs_arena_tma) {
-                  // blocked arena: one contiguous 4 KiB block per (source, tile, 64-column group,
-                  // 32-row quarter), rows of 128 bytes with their 16-byte chunks XOR-swizzled by row
-                  const size_t blk = ((((size_t)src * sched.tiles_per_chunk + ti.tile_in_chunk) * (BN / 64) + g) * 4 + quarter);
-                  add_row32_swizzled(p.rs_arena_local + (blk * 32 + lane) * ROW_BYTES, hf, lane, v, nvalid);
-                } else {
-                  const uint8_t* part = p.rs_arena_local + (((size_t)src * p.rs_slot_rows + chunk_row) * p.N[b] + col0) * oes;
-                  add_row32(part, v, nvalid, o32);
-                }
+                const uint8_t* part = p.rs_arena_local + (((size_t)src * p.rs_slot_rows + chunk_row) * p.N[b] + col0) * oes;
+                add_row32(part, v, nvalid, o32);
               }
             }
             if (p.reduce_scale != 1.0f) {
