@@ -5,18 +5,19 @@
 //               memory (all-gather mode), then streams A/B tiles into a shared-memory ring.
 //   warp 1      MMA issuer: one thread issues tcgen05.mma into a double-buffered TMEM
 //               accumulator (2 x BN fp32 columns).
-//   warps 2-5   epilogue: tcgen05.ld -> scale/bias/convert -> global. In reduce-scatter mode
-//               tiles owned by another rank are written straight into that rank's staging
-//               arena over NVLink and its per-tile flag is released; tiles owned by this rank
-//               are computed last and summed with the partials that arrived from the peers.
+//   warps 2-5   epilogue: tcgen05.ld -> scale/bias/convert -> swizzled shared-memory staging -> TMA
+//               store. In reduce-scatter mode a tile owned by another rank leaves as linear 4 KiB
+//               bulk copies into that rank's arena over NVLink and its per-tile flag is released
+//               (several tiles in flight, flags in pairs behind one system fence); tiles owned by
+//               this rank are computed last and summed with the partials that arrived.
 //   warps 6-11  communication (all-gather mode): stage the local shard in the symmetric
-//               buffer, tell the peers, then pull every peer's shard in ring order
-//               (rank+1, rank+2, ...) into the local gathered-A buffer in 4 KiB pieces,
-//               bumping a per-row-block counter the producer waits on.
+//               buffer, tell the peers, then pull the peers' shards into the local gathered-A
+//               buffer in 4 KiB pieces, bumping a per-row-block counter the producer waits on.
 //
-// The role of each chunk of rows follows the schedule of the reference's pipelines
-// (autoparallel/asynctp_ops.py:153-164 for all-gather: own shard first, then rank+step;
-// :250-321 for reduce-scatter: destination rank+step, own chunk last).
+// Like the reference's pipelines the local rank's rows are consumed first by the all-gather
+// (autoparallel/asynctp_ops.py:153) and produced last by the reduce-scatter (:321). Unlike them
+// (one peer per step, :155-164, :250-315) the peers' rows are interleaved row block by row block
+// so that a GPU exchanges data with all of its peers at once (see decode_tile).
 //
 // Every wait (mbarrier, flag, counter) is bounded by a cycle budget; when it runs out the
 // kernel records a code in the status word, raises a CTA-wide abort flag, drains its own
