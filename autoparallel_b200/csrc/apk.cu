@@ -278,7 +278,8 @@ uint64_t apk_gemm_rs_arena_bytes(const apk_gemm_rs_args* a, int32_t world) {
   // bf16 partials: whole tiles, stored as contiguous 32 x 64 blocks
   const uint64_t bn = a->B.N <= 128 ? 128 : 256;
   const uint64_t nt = ((uint64_t)a->B.N + bn - 1) / bn;
-  return (uint64_t)world * mt * nt * apk::BM * bn * 2;
+  // one slot per source rank, plus the fp32 sums of the peers' partials (twice a slot)
+  return (uint64_t)(world + 2) * mt * nt * apk::BM * bn * 2;
 }
 
 uint64_t apk_ctrl_bytes(int32_t rows_per_rank, int32_t world) {
@@ -458,6 +459,7 @@ int apk_gemm_rs(const apk_comm* comm, const apk_gemm_rs_args* a, void* stream_) 
     }
     kp.rs_arena_tma = a->B.out_dtype == APK_BF16;
     kp.rs_arena_local = kp.rs_arena_peer[comm->rank];
+    kp.rs_sum_local = reinterpret_cast<float*>(kp.rs_arena_local + (uint64_t)ws * tiles * apk::BM * bn * 2);
     kp.rs_flag_local = kp.rs_flag_peer[comm->rank];
   }
   return launch(kp, a->B.N, a->dtype == APK_E4M3, stream);

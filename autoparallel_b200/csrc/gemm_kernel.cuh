@@ -94,6 +94,7 @@ struct alignas(64) KParams {
   uint8_t* rs_arena_local;             // partials (current parity): bf16 blocked [ws][tile][BN/64][4][32][64],
                                        // fp32 row-major [ws][rs_slot_rows][N]
   uint8_t* rs_arena_peer[MAX_WORLD];
+  float* rs_sum_local;                 // bf16 partials: [tile][BN/64][4] blocks of 32 x 64 fp32 sums of the peers' partials
   uint32_t* rs_flag_local;             // [ws][rs_max_tiles]
   uint32_t* rs_flag_peer[MAX_WORLD];
   int32_t rs_max_tiles;
@@ -116,7 +117,7 @@ struct SmemLayout {
   static constexpr int BAR_OFF = STG_OFF + EPI_WARPS * STG_WARP_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 5;
   static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
-  static constexpr int TOTAL = MISC_OFF + 16 + 1024;  // + alignment slack
+  static constexpr int TOTAL = MISC_OFF + 32 + 1024;  // + alignment slack
 };
 
 struct TileInfo {
@@ -258,6 +259,29 @@ __device__ __forceinline__ bool flag_wait(const uint32_t* flag, uint32_t target,
   }
 }
 
+// Bounded wait until a shared-memory counter written by other warps of the CTA reaches `target`.
+__device__ __forceinline__ bool smem_count_wait(volatile uint32_t* ctr, uint32_t target, const KParams& p,
+                                                volatile uint32_t* abort_flag) {
+  uint32_t spins = 0;
+  long long t0 = 0;
+  while ((int32_t)(*ctr - target) < 0) {
+    if ((++spins & 0x3fu) == 0) {
+      if (*abort_flag) return false;
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > 2 * p.timeout_cycles) {   // the waiting warp it depends on reports first
+        set_status(p, ST_TIMEOUT_PARTIAL, 0xffu);
+        *abort_flag = 1;
+        return false;
+      }
+      __nanosleep(32);
+    }
+  }
+  __threadfence_block();
+  return true;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -357,6 +381,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + L::MISC_OFF);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFF + 4);
   volatile uint32_t* epi_verdict = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFF + 8);  // [2]
+  // reduce-scatter: how many of this CTA's own tiles have had their peers' partials summed
+  volatile uint32_t* sums_done = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFF + 16);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -374,6 +400,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
     }
     ptx::mbar_init(drain_bar, 1);
     *abort_flag = 0;
+    *sums_done = 0;
     ptx::fence_mbar_init();
   }
   if (warp == 1) {
@@ -550,6 +577,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       }
       ++pq_n;
     };
+    uint32_t own_seen = 0;   // own reduce-scatter tiles this CTA has finished
     uint32_t lt = 0;
     for (int t = blockIdx.x; t < sched.total_tiles; t += gridDim.x, ++lt) {
       const TileInfo ti = decode_tile<BN>(p, sched, t);
@@ -568,7 +596,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       // accumulator); its verdict is shared so that all four warps leave the loop together.
       if (epi_leader) {
         bool good = true;
-        if (p.mode == MODE_RS && own && p.ws > 1) {
+        if (p.mode == MODE_RS && own && p.ws > 1 && p.rs_arena_tma != 0) {
+          // the communication warps acquire the peers' flags and leave the sum of their partials
+          good = smem_count_wait(sums_done, own_seen + 1u, p, abort_flag);
+        } else if (p.mode == MODE_RS && own && p.ws > 1) {
           for (int src = 0; src < p.ws && good; ++src) {
             if (src == p.rank) continue;
             good = flag_wait<true>(p.rs_flag_local + (size_t)src * p.rs_max_tiles + ti.tile_in_chunk, p.epoch, p,
@@ -624,11 +655,39 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       for (int g = 0; g < BN / 64; ++g) {
         if (g * 64 >= ti.n_valid) break;   // uniform across the warp
         const uint32_t stg = stg_base + (stg_count & 1u) * (32 * ROW_BYTES);
-        if (use_tma) {
-          // the store that last used this buffer must have finished reading it
-          if (lane == 0) ptx::bulk_wait_group_read<1>();
+        // A tile this rank owns: the peers' bf16 partials of this 32-row x 64-column block are
+        // summed first, with coalesced loads (lane i takes 16-byte chunks i, i+32, ... of each
+        // 4 KiB block; row-per-thread loads reached a small fraction of the memory rate). The
+        // fp32 sums go through both staging buffers (8 KiB) so that each thread can pick up its row.
+        const bool own_blocked = (p.mode == MODE_RS) && own && p.ws > 1 && p.rs_arena_tma != 0;
+        if (use_tma || own_blocked) {
+          // the stores that last used the staging memory must have finished reading it
+          if (lane == 0) {
+            if (own_blocked) ptx::bulk_wait_group_read<0>(); else ptx::bulk_wait_group_read<1>();
+          }
           __syncwarp();
         }
+        if (own_blocked) {
+          // 8 KiB of fp32 sums for this warp's 32 rows x 64 columns, in the order of the bf16 blocks
+          // they were summed from: 16-byte unit U holds half h = U & 1 of chunk L = U >> 1, which is
+          // (row L / 8, stored position L % 8) = logical chunk (L % 8) ^ (row & 7). Coalesced loads,
+          // then a 256-byte fp32 row per thread in shared memory, XOR-swizzled against bank conflicts.
+          const uint8_t* sp = reinterpret_cast<const uint8_t*>(p.rs_sum_local) +
+                              ((((size_t)ti.tile_in_chunk * (BN / 64) + g) * 4 + quarter) * (size_t)(64 * ROW_BYTES));
+          uint4 u4[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) u4[i] = ptx::ld_cg_v4(sp + (size_t)(i * 32 + lane) * 16);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const uint32_t U = (uint32_t)(i * 32 + lane);
+            const uint32_t Lc = U >> 1, h = U & 1u;
+            const uint32_t row = Lc >> 3, sw = row & 7u;
+            const uint32_t c = (Lc & 7u) ^ sw;
+            ptx::st_shared_v4(stg_base + row * 256u + (((2u * c + h) ^ sw) << 4), u4[i].x, u4[i].y, u4[i].z, u4[i].w);
+          }
+          __syncwarp();
+        }
+        uint32_t packed[2][16];
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
           const int c = g * 2 + hf;
@@ -680,42 +739,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
             }
           }
           if (p.mode == MODE_RS && own) {
-            if (row_ok && p.rs_arena_tma) {
-              // Blocked arena: one contiguous 4 KiB block per (source, tile, 64-column group, 32-row
-              // quarter), rows of 128 bytes whose 16-byte chunks are XOR-swizzled by row. The loads
-              // of four sources are issued before any of them is consumed: a thread that waited for
-              // one source at a time would pay a memory latency per source.
-              const size_t blk0 = (((size_t)ti.tile_in_chunk * (BN / 64) + g) * 4 + quarter) * 32 + lane;
-              const size_t src_stride = (size_t)sched.tiles_per_chunk * (BN / 64) * 4 * 32;
-              for (int s0 = 0; s0 < p.ws; s0 += 4) {
-                uint4 q[4][4];
+            if (own_blocked) {
+              // this thread's row of the fp32 sums, half `hf`
+              const uint32_t sw = (uint32_t)(lane & 7);
+              const uint32_t base = stg_base + (uint32_t)lane * 256u;
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                  const int src = s0 + u;
-                  if (src < p.ws && src != p.rank) {
-                    const uint8_t* row = p.rs_arena_local + (blk0 + (size_t)src * src_stride) * ROW_BYTES;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                      const uint32_t chunk = (uint32_t)(hf * 4 + j) ^ (uint32_t)(lane & 7);
-                      q[u][j] = (j * 8 < nvalid) ? __ldcg(reinterpret_cast<const uint4*>(row + chunk * 16)) : make_uint4(0, 0, 0, 0);
-                    }
-                  }
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                  const int src = s0 + u;
-                  if (src < p.ws && src != p.rank) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                      const uint32_t w[4] = {q[u][j].x, q[u][j].y, q[u][j].z, q[u][j].w};
-#pragma unroll
-                      for (int e = 0; e < 4; ++e) {
-                        v[8 * j + 2 * e] += __uint_as_float(w[e] << 16);
-                        v[8 * j + 2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
-                      }
-                    }
-                  }
-                }
+              for (int j = 0; j < 4; ++j) {
+                const uint32_t c = (uint32_t)(hf * 4 + j);
+                const float4 s0 = ptx::ld_shared_f4(base + (((2u * c) ^ sw) << 4));
+                const float4 s1 = ptx::ld_shared_f4(base + (((2u * c + 1u) ^ sw) << 4));
+                v[8 * j + 0] += s0.x; v[8 * j + 1] += s0.y; v[8 * j + 2] += s0.z; v[8 * j + 3] += s0.w;
+                v[8 * j + 4] += s1.x; v[8 * j + 5] += s1.y; v[8 * j + 6] += s1.z; v[8 * j + 7] += s1.w;
               }
             } else if (row_ok) {
               for (int src = 0; src < p.ws; ++src) {
@@ -730,14 +764,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
             }
           }
           if (use_tma) {
-            // 16-byte chunk j of this thread's row goes where the 128-byte swizzle expects it
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t chunk = (uint32_t)(hf * 4 + j) ^ (uint32_t)(lane & 7);
-              ptx::st_shared_v4(stg + lane * ROW_BYTES + chunk * 16,
-                                pack_bf16(v[8 * j + 0], v[8 * j + 1]), pack_bf16(v[8 * j + 2], v[8 * j + 3]),
-                                pack_bf16(v[8 * j + 4], v[8 * j + 5]), pack_bf16(v[8 * j + 6], v[8 * j + 7]));
-            }
+            for (int j = 0; j < 16; ++j) packed[hf][j] = pack_bf16(v[2 * j], v[2 * j + 1]);
           } else if (row_ok) {
             uint8_t* dst;
             if (rs_remote) {
@@ -751,6 +779,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
           }
         }
         if (use_tma) {
+          if (own_blocked) __syncwarp();   // every lane has read its sums: the buffer may be reused
+          // 16-byte chunk c of this thread's row goes where the 128-byte swizzle expects it
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            if ((g * 2 + hf) * 32 >= ti.n_valid) break;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t chunk = (uint32_t)(hf * 4 + j) ^ (uint32_t)(lane & 7);
+              ptx::st_shared_v4(stg + lane * ROW_BYTES + chunk * 16, packed[hf][4 * j], packed[hf][4 * j + 1],
+                                packed[hf][4 * j + 2], packed[hf][4 * j + 3]);
+            }
+          }
           ptx::fence_proxy_async_shared();
           __syncwarp();
           if (lane == 0) {
@@ -773,6 +813,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
 
+      if (p.mode == MODE_RS && own) ++own_seen;
       if (rs_remote) {
         // The owner's flag for this tile is released once three newer tiles are queued behind it,
         // before this CTA waits on its peers, or after the loop.
@@ -783,7 +824,78 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
     if (lane == 0) ptx::bulk_wait_group<0>();   // shared memory must outlive the last stores
     __syncwarp();
   } else {
-    // ============================================================ communication warps (all-gather)
+    // ============================================================ communication warps
+    if (p.mode == MODE_RS && p.ws > 1 && p.rs_arena_tma != 0) {
+      // Reduce-scatter: for every tile of this CTA that the local rank owns, wait for the peers'
+      // partials, add them up block by block (coalesced 16-byte loads, two peers in flight per
+      // warp) and leave the fp32 sums for the epilogue. This runs while the epilogue warps are
+      // still busy sending other ranks' tiles.
+      const int cw = warp - (2 + EPI_WARPS);
+      const size_t src_stride = (size_t)sched.tiles_per_chunk * (BN / 64) * 4 * (32 * ROW_BYTES);
+      const int remote_tiles = sched.tiles_per_chunk * (p.ws - 1);
+      uint32_t done = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < sched.total_tiles && ok; t += gridDim.x) {
+        if (t < remote_tiles) continue;
+        const TileInfo ti = decode_tile<BN>(p, sched, t);
+        if (cw == 0) {
+          if (lane == 0) {
+            for (int src = 0; src < p.ws && ok; ++src) {
+              if (src == p.rank) continue;
+              ok = flag_wait<true>(p.rs_flag_local + (size_t)src * p.rs_max_tiles + ti.tile_in_chunk, p.epoch, p,
+                                   abort_flag, ST_TIMEOUT_PARTIAL, (uint32_t)src);
+            }
+          }
+        }
+        ptx::named_bar_sync(3, COMM_WARPS * 32);
+        if (*abort_flag) break;
+        const int groups = (ti.n_valid + 63) / 64;
+        for (int blk16 = cw; blk16 < groups * 4; blk16 += COMM_WARPS) {
+          const size_t blk = ((size_t)ti.tile_in_chunk * (BN / 64) * 4 + blk16);
+          const uint8_t* base = p.rs_arena_local + blk * (32 * ROW_BYTES);
+          float sum[64];
+#pragma unroll
+          for (int j = 0; j < 64; ++j) sum[j] = 0.0f;
+          for (int s0 = 1; s0 < p.ws; s0 += 2) {
+            uint4 q[2][8];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              if (s0 + u < p.ws) {
+                const uint8_t* bp = base + (size_t)((p.rank + s0 + u) % p.ws) * src_stride;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) q[u][i] = ptx::ld_cg_v4(bp + (size_t)(i * 32 + lane) * 16);
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              if (s0 + u < p.ws) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const uint32_t w[4] = {q[u][i].x, q[u][i].y, q[u][i].z, q[u][i].w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    sum[8 * i + 2 * e] += __uint_as_float(w[e] << 16);
+                    sum[8 * i + 2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+                  }
+                }
+              }
+            }
+          }
+          // chunk L = i*32+lane of the bf16 block becomes units 2L and 2L+1 of the 8 KiB fp32 block
+          float4* op = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(p.rs_sum_local) + blk * (size_t)(64 * ROW_BYTES));
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int Lc = i * 32 + lane;
+            op[2 * Lc] = make_float4(sum[8 * i], sum[8 * i + 1], sum[8 * i + 2], sum[8 * i + 3]);
+            op[2 * Lc + 1] = make_float4(sum[8 * i + 4], sum[8 * i + 5], sum[8 * i + 6], sum[8 * i + 7]);
+          }
+        }
+        __threadfence();
+        ptx::named_bar_sync(3, COMM_WARPS * 32);
+        ++done;
+        if (cw == 0 && lane == 0) *sums_done = done;
+      }
+    }
     if (p.mode == MODE_AG) {
       const int cw = warp - (2 + EPI_WARPS);
       const int gw = blockIdx.x * COMM_WARPS + cw;

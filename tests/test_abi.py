@@ -52,7 +52,8 @@ def test_workspace_size_helpers(L):
     assert L.apk_ag_gemm_arena_bytes(C.byref(a), 8) == 4096 * 4096 + 4096 * 4
     r = nat.ApkGemmRsArgs()
     r.M, r.B.N, r.B.out_dtype = 32768, 4096, nat.APK_BF16
-    assert L.apk_gemm_rs_arena_bytes(C.byref(r), 8) == 32768 * 4096 * 2  # 8 ranks x 32 x 16 tiles of 128 x 256 bf16
+    # 8 source slots of 32 x 16 bf16 tiles of 128 x 256, plus fp32 sums of one slot (= 2 bf16 slots)
+    assert L.apk_gemm_rs_arena_bytes(C.byref(r), 8) == (8 + 2) * 4096 * 4096 * 2
     assert L.apk_ctrl_bytes(4096, 8) == 256 + 4 * 32 * 8
 
 

@@ -351,7 +351,7 @@ def test_reduce_scatter_receive_side_on_one_gpu(group, world, M, K, N):
     args0 = nat.ApkGemmRsArgs()
     args0.M, args0.B.N, args0.B.out_dtype = M, N, nat.APK_BF16
     half = int(L.apk_gemm_rs_arena_bytes(C.byref(args0), world))
-    slot = half // world
+    slot = half // (world + 2)   # world source slots, then the fp32 sums (two slots' worth)
     arenas = [torch.zeros(2 * half, dtype=torch.uint8, device="cuda") for _ in range(world)]
     for h in range(2):
         for src in range(1, world):
@@ -405,7 +405,7 @@ def test_device_wait_times_out_cleanly(group):
     A = orc.activations(0, M, K).cuda()
     B = orc.weights(7, K, N).cuda()
     out = torch.empty(M // 2, N, dtype=torch.bfloat16, device="cuda")
-    arena = torch.zeros(2 * 2 * 128 * 128, dtype=torch.bfloat16, device="cuda")  # two halves of [2 ranks][1 tile of 128x128]
+    arena = torch.zeros(2 * 4 * 128 * 128, dtype=torch.bfloat16, device="cuda")  # two halves of [2 rank slots + fp32 sums][1 tile of 128x128]
     flags = torch.zeros(8192 * 2, dtype=torch.int32, device="cuda")
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
     ctrl = torch.zeros(1024, dtype=torch.int32, device="cuda")
