@@ -320,8 +320,8 @@ def run_ours(args) -> None:
 
 
 # DRAM bytes (read + write) of one all-gather-mode launch at this workload, from the ncu capture
-# summarised in profiles/; None until a capture exists.
-TRAFFIC_AG_BYTES = None
+# summarised in profiles/ (8192-token capture scaled to 32768 tokens: A and outputs scale, B does not).
+TRAFFIC_AG_BYTES = 305.6e6 + 161.3e6
 
 
 def main():
