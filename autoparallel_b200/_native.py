@@ -51,6 +51,7 @@ EXPORTED_SYMBOLS = (
     "apk_ag_gemm_static",
     "apk_check_status",
     "apk_launch_count",
+    "apk_pair_launch_count",
 )
 
 
@@ -161,6 +162,7 @@ def lib() -> C.CDLL:
     L.apk_ag_gemm_static.restype = C.c_int
     L.apk_check_status.argtypes = [C.POINTER(ApkComm), C.c_void_p, C.POINTER(C.c_uint32)]
     L.apk_launch_count.restype = C.c_uint64
+    L.apk_pair_launch_count.restype = C.c_uint64
     for name in ("apk_symm_alloc", "apk_symm_free", "apk_symm_export", "apk_symm_import", "apk_symm_unimport",
                  "apk_ag_gemm", "apk_gemm_rs", "apk_check_status"):
         getattr(L, name).restype = C.c_int

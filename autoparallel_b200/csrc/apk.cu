@@ -7,6 +7,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -17,6 +18,7 @@ namespace {
 
 thread_local char g_err[512] = "";
 std::atomic<uint64_t> g_launches{0};
+std::atomic<uint64_t> g_pair_launches{0};
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -96,11 +98,12 @@ int device_info(DeviceInfo* out) {
   return APK_OK;
 }
 
-template <int BN, int STAGES, bool FP8>
-int launch_instance(const apk::KParams& kp, int grid, cudaStream_t stream) {
-  using L = apk::SmemLayout<BN, STAGES>;
-  auto kern = apk::gemm_fused_kernel<BN, STAGES, FP8>;
+template <int BN, int STAGES, bool FP8, bool PAIR>
+int launch_instance(const apk::KParams& kp, long long units, const DeviceInfo& di, cudaStream_t stream) {
+  using L = apk::SmemLayout<BN, STAGES, PAIR>;
+  auto kern = apk::gemm_fused_kernel<BN, STAGES, FP8, PAIR>;
   static bool configured[64] = {};
+  static int max_clusters[64] = {};
   int dev = 0;
   APK_CUDA(cudaGetDevice(&dev));
   if (!configured[dev]) {
@@ -108,20 +111,58 @@ int launch_instance(const apk::KParams& kp, int grid, cudaStream_t stream) {
     configured[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3(apk::NUM_THREADS);
   cfg.dynamicSmemBytes = L::TOTAL;
   cfg.stream = stream;
   // Cooperative: all CTAs must be resident at once, because the communication warps of every
   // CTA feed row blocks that other CTAs' producers wait for.
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeCooperative;
   attr[0].val.cooperative = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (PAIR) {
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+    if (max_clusters[dev] == 0) {
+      cfg.gridDim = dim3((unsigned)(di.sms & ~1));
+      int n = 0;
+      cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+      if (e != cudaSuccess || n < 1) {
+        cudaGetLastError();
+        return fail(APK_ERR_CUDA, "CTA pairs cannot be scheduled on this device (%s)", cudaGetErrorString(e));
+      }
+      max_clusters[dev] = n;
+      if (getenv("APK_VERBOSE") != nullptr) fprintf(stderr, "[apk] device %d: %d SMs, at most %d co-resident CTA pairs\n", dev, di.sms, n);
+    }
+    const long long clusters = units < max_clusters[dev] ? units : max_clusters[dev];
+    cfg.gridDim = dim3((unsigned)(2 * clusters));
+  } else {
+    cfg.gridDim = dim3((unsigned)(units < di.sms ? units : di.sms));
+  }
   APK_CUDA(cudaLaunchKernelEx(&cfg, kern, kp));
   g_launches.fetch_add(1);
+  if (PAIR) g_pair_launches.fetch_add(1);
   return APK_OK;
+}
+
+// CTA pairs (cta_group::2) are used when every output is a whole number of 256-column tiles and every
+// chunk a whole number of 256-row tile pairs; APK_PAIR=0 in the environment turns them off.
+bool pair_eligible(const apk::KParams& kp) {
+  static int env = -1;
+  if (env < 0) {
+    const char* e = getenv("APK_PAIR");
+    env = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  if (!env) return false;
+  for (int b = 0; b < kp.nB; ++b) {
+    if (kp.N[b] % 256 != 0) return false;
+  }
+  const long long mt = (kp.rows_per_rank + apk::BM - 1) / apk::BM;
+  return mt % 2 == 0;
 }
 
 int launch(const apk::KParams& kp, int max_n, bool fp8, cudaStream_t stream) {
@@ -133,14 +174,22 @@ int launch(const apk::KParams& kp, int max_n, bool fp8, cudaStream_t stream) {
   long long nt = 0;
   for (int b = 0; b < kp.nB; ++b) nt += (kp.N[b] + bn - 1) / bn;
   const long long mt = (kp.rows_per_rank + apk::BM - 1) / apk::BM;
-  const long long tiles = nt * mt * (kp.mode == apk::MODE_PLAIN ? 1 : kp.ws);
+  const long long chunks = kp.mode == apk::MODE_PLAIN ? 1 : kp.ws;
+  const long long tiles = nt * mt * chunks;
   if (tiles <= 0) return APK_OK;
   if (tiles > 0x7fffffffLL) return fail(APK_ERR_ARG, "too many tiles");
-  const int grid = (int)(tiles < di.sms ? tiles : di.sms);
-  if (narrow) {
-    return fp8 ? launch_instance<128, 6, true>(kp, grid, stream) : launch_instance<128, 6, false>(kp, grid, stream);
+  static bool pair_failed = false;
+  if (!narrow && !pair_failed && pair_eligible(kp)) {
+    rc = fp8 ? launch_instance<256, 6, true, true>(kp, tiles / 2, di, stream)
+             : launch_instance<256, 6, false, true>(kp, tiles / 2, di, stream);
+    if (rc == APK_OK) return rc;
+    pair_failed = true;   // e.g. cooperative cluster launches unsupported: use single CTAs from now on
+    cudaGetLastError();
   }
-  return fp8 ? launch_instance<256, 4, true>(kp, grid, stream) : launch_instance<256, 4, false>(kp, grid, stream);
+  if (narrow) {
+    return fp8 ? launch_instance<128, 6, true, false>(kp, tiles, di, stream) : launch_instance<128, 6, false, false>(kp, tiles, di, stream);
+  }
+  return fp8 ? launch_instance<256, 4, true, false>(kp, tiles, di, stream) : launch_instance<256, 4, false, false>(kp, tiles, di, stream);
 }
 
 uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
@@ -160,6 +209,8 @@ int fill_operand(apk::KParams* kp, int b, const apk_operand& op, int dtype, int 
     rc = encode_2d(&kp->tmB[b], dtype, op.B, (uint64_t)op.N, (uint64_t)K, (uint64_t)op.ldb, bke, bke, what);
   } else {
     rc = encode_2d(&kp->tmB[b], dtype, op.B, (uint64_t)K, (uint64_t)op.N, (uint64_t)op.ldb, bke, bn, what);
+    if (rc == APK_OK && bn == 256)   // a CTA of a pair loads 128 of the tile's 256 columns
+      rc = encode_2d(&kp->tmBp[b], dtype, op.B, (uint64_t)K, (uint64_t)op.N, (uint64_t)op.ldb, bke, bn / 2, what);
   }
   if (rc != APK_OK) return rc;
   kp->N[b] = op.N;
@@ -213,6 +264,7 @@ extern "C" {
 int apk_abi_version(void) { return APK_ABI_VERSION; }
 const char* apk_last_error(void) { return g_err; }
 uint64_t apk_launch_count(void) { return g_launches.load(); }
+uint64_t apk_pair_launch_count(void) { return g_pair_launches.load(); }
 
 int apk_symm_alloc(uint64_t bytes, void** ptr) {
   if (ptr == nullptr || bytes == 0) return fail(APK_ERR_ARG, "apk_symm_alloc: bad arguments");

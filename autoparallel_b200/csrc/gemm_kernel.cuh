@@ -57,6 +57,7 @@ struct alignas(64) KParams {
   CUtensorMap tmA0;            // plain / RS: all of A. AG: the local shard [rows_per_rank, K]
   CUtensorMap tmA1;            // AG: the gathered A [M, K]
   CUtensorMap tmB[MAX_B];
+  CUtensorMap tmBp[MAX_B];             // CTA pairs, K-contiguous B: box of BN/2 rows (each CTA loads half of N)
   CUtensorMap tmOut[MAX_B];            // bf16 outputs, box 32 rows x 64 columns (TMA stores)
   int32_t mode, ws, rank, nB;
   int32_t M, K, rows_per_rank, elem_bytes;
@@ -107,10 +108,10 @@ struct alignas(64) KParams {
   long long timeout_cycles;
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool PAIR = false>
 struct SmemLayout {
   static constexpr int A_BYTES = BM * ROW_BYTES;
-  static constexpr int B_BYTES = BN * ROW_BYTES;
+  static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * ROW_BYTES;   // a CTA of a pair holds half of B's columns
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STG_OFF = STAGES * STAGE_BYTES;              // epilogue staging, 1024-aligned
   static constexpr int STG_WARP_BYTES = 2 * 32 * ROW_BYTES;         // two 32-row x 128-byte buffers per warp
@@ -134,12 +135,13 @@ struct Sched {
   int nt_b[MAX_B];
   int nt_total;
   int mt_per_chunk;
-  int tiles_per_chunk;
+  int tiles_per_chunk;   // 128-row tiles per chunk (indexing of flags and arena blocks)
+  int units_per_chunk;   // scheduling units per chunk: tiles, or pairs of vertically adjacent tiles
   int num_chunks;
-  int total_tiles;
+  int total_tiles;       // scheduling units in the whole problem
 };
 
-template <int BN>
+template <int BN, bool PAIR = false>
 __device__ __forceinline__ Sched make_sched(const KParams& p) {
   Sched s;
   s.nt_total = 0;
@@ -150,8 +152,9 @@ __device__ __forceinline__ Sched make_sched(const KParams& p) {
   }
   s.mt_per_chunk = (p.rows_per_rank + BM - 1) / BM;
   s.tiles_per_chunk = s.mt_per_chunk * s.nt_total;
+  s.units_per_chunk = (PAIR ? s.mt_per_chunk / 2 : s.mt_per_chunk) * s.nt_total;
   s.num_chunks = (p.mode == MODE_PLAIN) ? 1 : p.ws;
-  s.total_tiles = s.tiles_per_chunk * s.num_chunks;
+  s.total_tiles = s.units_per_chunk * s.num_chunks;
   return s;
 }
 
@@ -161,8 +164,9 @@ __device__ __forceinline__ Sched make_sched(const KParams& p) {
 // so that at any moment a GPU exchanges data with all of its peers at once. On an NVSwitch
 // fabric this keeps every GPU's ingress and egress busy even when the ranks drift apart,
 // which a strict "one peer per step" order does not.
-template <int BN>
-__device__ __forceinline__ TileInfo decode_tile(const KParams& p, const Sched& s, int t) {
+// With PAIR a unit is two vertically adjacent tiles (same columns); `crank` (0 or 1) picks this CTA's.
+template <int BN, bool PAIR = false>
+__device__ __forceinline__ TileInfo decode_tile(const KParams& p, const Sched& s, int t, int crank = 0) {
   TileInfo ti;
   int nt;
   if (p.mode == MODE_PLAIN || p.ws == 1) {
@@ -170,15 +174,15 @@ __device__ __forceinline__ TileInfo decode_tile(const KParams& p, const Sched& s
     ti.mt = t / s.nt_total;
     nt = t - ti.mt * s.nt_total;
   } else {
-    const int remote_tiles = s.tiles_per_chunk * (p.ws - 1);
-    const bool own = (p.mode == MODE_AG) ? (t < s.tiles_per_chunk) : (t >= remote_tiles);
+    const int remote_tiles = s.units_per_chunk * (p.ws - 1);
+    const bool own = (p.mode == MODE_AG) ? (t < s.units_per_chunk) : (t >= remote_tiles);
     if (own) {
       const int r = (p.mode == MODE_AG) ? t : t - remote_tiles;
       ti.chunk = p.rank;
       ti.mt = r / s.nt_total;
       nt = r - ti.mt * s.nt_total;
     } else {
-      const int r = (p.mode == MODE_AG) ? t - s.tiles_per_chunk : t;
+      const int r = (p.mode == MODE_AG) ? t - s.units_per_chunk : t;
       const int per_mt = s.nt_total * (p.ws - 1);
       ti.mt = r / per_mt;
       const int rr = r - ti.mt * per_mt;
@@ -187,6 +191,7 @@ __device__ __forceinline__ TileInfo decode_tile(const KParams& p, const Sched& s
       ti.chunk = (p.rank + 1 + step) % p.ws;
     }
   }
+  if (PAIR) ti.mt = 2 * ti.mt + crank;
   ti.tile_in_chunk = ti.mt * s.nt_total + nt;
   ti.b = 0;
 #pragma unroll
@@ -360,9 +365,14 @@ __device__ __forceinline__ void copy_piece(const uint8_t* src, uint8_t* dst, uin
   }
 }
 
-template <int BN, int STAGES, bool FP8>
+// PAIR: the grid is made of clusters of two CTAs; a pair works on two vertically adjacent tiles
+// (256 rows x BN columns) with one tcgen05.mma.cta_group::2 stream issued by the CTA of cluster
+// rank 0. Each CTA loads its own 128 rows of A and HALF of B's columns (32 KiB instead of 48 KiB
+// per k-block from L2, the bound of the single-CTA kernel), keeps its 128 x BN accumulator in its
+// own TMEM and runs its own epilogue and communication warps exactly as without PAIR.
+template <int BN, int STAGES, bool FP8, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid_constant__ KParams p) {
-  using L = SmemLayout<BN, STAGES>;
+  using L = SmemLayout<BN, STAGES, PAIR>;
   constexpr int BKE = FP8 ? 128 : 64;           // K elements per stage (128 bytes)
   constexpr int UMMA_K = FP8 ? 32 : 16;         // K elements per tcgen05.mma (32 bytes)
   constexpr int KSTEPS = BKE / UMMA_K;          // 4
@@ -386,17 +396,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const Sched sched = make_sched<BN>(p);
+  const Sched sched = make_sched<BN, PAIR>(p);
+  const int crank = PAIR ? (int)ptx::cluster_ctarank() : 0;          // rank inside the pair
+  const int tile_first = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int tile_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   const int num_kb = (p.K + BKE - 1) / BKE;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(full_bar(s), PAIR ? 2 : 1);   // pair: both CTAs' producers arrive on rank 0's barrier
       ptx::mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(tfull_bar(a), 1);
-      ptx::mbar_init(tempty_bar(a), EPI_WARPS);
+      ptx::mbar_init(tempty_bar(a), PAIR ? 2 * EPI_WARPS : EPI_WARPS);   // pair: both CTAs' epilogues
     }
     ptx::mbar_init(drain_bar, 1);
     *abort_flag = 0;
@@ -404,11 +417,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
     ptx::fence_mbar_init();
   }
   if (warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(tmem_ptr_smem), TMEM_COLS);
-    ptx::tmem_relinquish();
+    if (PAIR) {
+      ptx::tmem_alloc_pair(ptx::smem_u32(tmem_ptr_smem), TMEM_COLS);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(ptx::smem_u32(tmem_ptr_smem), TMEM_COLS);
+      ptx::tmem_relinquish();
+    }
   }
   ptx::tc_fence_before();
-  __syncthreads();
+  if (PAIR) ptx::cluster_sync(); else __syncthreads();   // pair: the other CTA's barriers are initialised too
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
@@ -420,8 +438,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       for (int b = 0; b < p.nB; ++b) ptx::tma_prefetch_desc(&p.tmB[b]);
       uint32_t it = 0;       // k-block counter over the CTA's lifetime
       bool ok = true;
-      for (int t = blockIdx.x; t < sched.total_tiles && ok; t += gridDim.x) {
-        const TileInfo ti = decode_tile<BN>(p, sched, t);
+      for (int t = tile_first; t < sched.total_tiles && ok; t += tile_step) {
+        const TileInfo ti = decode_tile<BN, PAIR>(p, sched, t, crank);
         const CUtensorMap* tmA = &p.tmA0;
         int arow = ti.mt * BM;
         if (p.mode == MODE_AG && ti.chunk != p.rank) {
@@ -444,20 +462,36 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
           if (!ok) break;
           const uint32_t a_dst = smem_base + s * L::STAGE_BYTES;
           const uint32_t b_dst = a_dst + L::A_BYTES;
-          ptx::mbar_expect_tx(full_bar(s), L::STAGE_BYTES);
-          ptx::tma_load_2d(a_dst, tmA, full_bar(s), kb * BKE, arow);
-          if (!nmajor) {
-            ptx::tma_load_2d(b_dst, tmB, full_bar(s), kb * BKE, ti.n0);
-          } else {
+          if (PAIR) {
+            // this CTA's A rows and its half of B's columns; bytes are counted on rank 0's barrier
+            const uint32_t fb = ptx::mapa(full_bar(s), 0);
+            const int nb = ti.n0 + crank * (BN / 2);
+            ptx::mbar_expect_tx_cluster(fb, L::STAGE_BYTES);
+            ptx::tma_load_2d_pair(a_dst, tmA, fb, kb * BKE, arow);
+            if (!nmajor) {
+              ptx::tma_load_2d_pair(b_dst, &p.tmBp[ti.b], fb, kb * BKE, nb);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BN / NPB; ++j) {
-              ptx::tma_load_2d(b_dst + j * (BKE * ROW_BYTES), tmB, full_bar(s), ti.n0 + j * NPB, kb * BKE);
+              for (int j = 0; j < BN / 2 / NPB; ++j) {
+                ptx::tma_load_2d_pair(b_dst + j * (BKE * ROW_BYTES), tmB, fb, nb + j * NPB, kb * BKE);
+              }
+            }
+          } else {
+            ptx::mbar_expect_tx(full_bar(s), L::STAGE_BYTES);
+            ptx::tma_load_2d(a_dst, tmA, full_bar(s), kb * BKE, arow);
+            if (!nmajor) {
+              ptx::tma_load_2d(b_dst, tmB, full_bar(s), kb * BKE, ti.n0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / NPB; ++j) {
+                ptx::tma_load_2d(b_dst + j * (BKE * ROW_BYTES), tmB, full_bar(s), ti.n0 + j * NPB, kb * BKE);
+              }
             }
           }
         }
       }
       // Drain: every load this thread armed has either landed or is given a bounded time to.
-      const uint32_t last = it;
+      const uint32_t last = (PAIR && crank != 0) ? 0u : it;   // (rank 1 of a pair has no full barriers of its own)
       const uint32_t first = last > (uint32_t)STAGES ? last - STAGES : 0u;
       for (uint32_t i = first; i < last; ++i) {
         const int s = i % STAGES;
@@ -470,7 +504,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
     __syncwarp();
   } else if (warp == 1) {
     // ============================================================ MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && crank == 0) {
       // Shared-memory matrix descriptor: version 1 (bit 46), 128-byte swizzle (2 << 61),
       // stride byte offset 1024 (8 rows x 128 B) in 16-byte units at bit 32.
       const uint64_t desc_common = (uint64_t(1) << 46) | (uint64_t(2) << 61) | (uint64_t(1024 >> 4) << 32);
@@ -478,19 +512,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       const uint64_t desc_nmajor = desc_common | (uint64_t((BKE * ROW_BYTES) >> 4) << 16);
       // Instruction descriptor: fp32 accumulate, A/B format (bf16 = 1, e4m3 = 0), M = 128.
       const uint32_t fmt = FP8 ? 0u : 1u;
-      const uint32_t idesc_base = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(BM >> 4) << 24);
+      const uint32_t idesc_base = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t((PAIR ? 2 * BM : BM) >> 4) << 24);
       uint32_t it = 0;
       uint32_t lt = 0;  // local tile counter
       bool ok = true;
-      for (int t = blockIdx.x; t < sched.total_tiles && ok; t += gridDim.x, ++lt) {
-        const TileInfo ti = decode_tile<BN>(p, sched, t);
+      for (int t = tile_first; t < sched.total_tiles && ok; t += tile_step, ++lt) {
+        const TileInfo ti = decode_tile<BN, PAIR>(p, sched, t, crank);
         const uint32_t acc = lt & 1u;
         const uint32_t aph = (lt >> 1) & 1u;
         ok = mbar_wait(tempty_bar(acc), aph ^ 1u, p, abort_flag);
         if (!ok) break;
         ptx::tc_fence_after();
         const bool nmajor = p.b_nmajor[ti.b] != 0;
-        const int n_eff = min(BN, (ti.n_valid + 15) & ~15);
+        const int n_eff = PAIR ? BN : min(BN, (ti.n_valid + 15) & ~15);   // a pair splits N evenly, so it is fixed
         const uint32_t idesc = idesc_base | (nmajor ? (1u << 16) : 0u) | (uint32_t(n_eff >> 3) << 17);
         const uint32_t d_tmem = tmem_base + acc * BN;
         const uint64_t bdesc_hi = nmajor ? desc_nmajor : desc_kmajor;
@@ -508,18 +542,33 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
 #pragma unroll
           for (int k = 0; k < KSTEPS; ++k) {
             const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
-            if (FP8) {
+            if (PAIR) {
+              if (FP8) ptx::mma_f8_pair(d_tmem, adesc + 2u * k, bdesc + bstep * k, idesc, accum);
+              else ptx::mma_f16_pair(d_tmem, adesc + 2u * k, bdesc + bstep * k, idesc, accum);
+            } else if (FP8) {
               ptx::mma_f8(d_tmem, adesc + 2u * k, bdesc + bstep * k, idesc, accum);
             } else {
               ptx::mma_f16(d_tmem, adesc + 2u * k, bdesc + bstep * k, idesc, accum);
             }
           }
-          ptx::tc_commit(empty_bar(s));
+          if (PAIR) {   // the stage is free again in both CTAs
+            ptx::tc_commit_pair(ptx::mapa(empty_bar(s), 0));
+            ptx::tc_commit_pair(ptx::mapa(empty_bar(s), 1));
+          } else {
+            ptx::tc_commit(empty_bar(s));
+          }
         }
-        if (ok) ptx::tc_commit(tfull_bar(acc));
+        if (ok) {
+          if (PAIR) {
+            ptx::tc_commit_pair(ptx::mapa(tfull_bar(acc), 0));
+            ptx::tc_commit_pair(ptx::mapa(tfull_bar(acc), 1));
+          } else {
+            ptx::tc_commit(tfull_bar(acc));
+          }
+        }
       }
       // Make sure nothing this thread issued is still running before TMEM is freed.
-      ptx::tc_commit(drain_bar);
+      if (PAIR) ptx::tc_commit_pair(ptx::mapa(drain_bar, 0)); else ptx::tc_commit(drain_bar);
       uint32_t spins = 0;
       while (!ptx::mbar_try_wait(drain_bar, 0) && ++spins < (1u << 20)) {
       }
@@ -579,8 +628,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
     };
     uint32_t own_seen = 0;   // own reduce-scatter tiles this CTA has finished
     uint32_t lt = 0;
-    for (int t = blockIdx.x; t < sched.total_tiles; t += gridDim.x, ++lt) {
-      const TileInfo ti = decode_tile<BN>(p, sched, t);
+    for (int t = tile_first; t < sched.total_tiles; t += tile_step, ++lt) {
+      const TileInfo ti = decode_tile<BN, PAIR>(p, sched, t, crank);
       const uint32_t acc = lt & 1u;
       const uint32_t aph = (lt >> 1) & 1u;
       const bool row_ok = row_in_tile < ti.rows_valid;
@@ -811,7 +860,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       // Release the accumulator to the MMA warp.
       ptx::tc_fence_before();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+      if (lane == 0) {
+        if (PAIR) ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(acc), 0)); else ptx::mbar_arrive(tempty_bar(acc));
+      }
 
       if (p.mode == MODE_RS && own) ++own_seen;
       if (rs_remote) {
@@ -832,12 +883,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       // still busy sending other ranks' tiles.
       const int cw = warp - (2 + EPI_WARPS);
       const size_t src_stride = (size_t)sched.tiles_per_chunk * (BN / 64) * 4 * (32 * ROW_BYTES);
-      const int remote_tiles = sched.tiles_per_chunk * (p.ws - 1);
+      const int remote_tiles = sched.units_per_chunk * (p.ws - 1);
       uint32_t done = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < sched.total_tiles && ok; t += gridDim.x) {
+      for (int t = tile_first; t < sched.total_tiles && ok; t += tile_step) {
         if (t < remote_tiles) continue;
-        const TileInfo ti = decode_tile<BN>(p, sched, t);
+        const TileInfo ti = decode_tile<BN, PAIR>(p, sched, t, crank);
         if (cw == 0) {
           if (lane == 0) {
             for (int src = 0; src < p.ws && ok; ++src) {
@@ -1018,10 +1069,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
 
   // ============================================================ teardown
   ptx::tc_fence_before();
-  __syncthreads();
+  if (PAIR) ptx::cluster_sync(); else __syncthreads();   // pair: nobody signals a CTA that has left
   if (warp == 1) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    if (PAIR) ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS); else ptx::tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 

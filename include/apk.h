@@ -183,6 +183,8 @@ int apk_check_status(const apk_comm* comm, void* stream, uint32_t* raw);
 
 /* Kernels launched by this library in this process so far (memsets not counted). */
 uint64_t apk_launch_count(void);
+/* ... of which launched as clusters of two CTAs (tcgen05 cta_group::2). */
+uint64_t apk_pair_launch_count(void);
 
 #ifdef __cplusplus
 }
