@@ -40,6 +40,7 @@ constexpr int EPI_WARPS = 4;
 constexpr int COMM_WARPS = 6;
 constexpr int NUM_THREADS = 32 * (2 + EPI_WARPS + COMM_WARPS);
 constexpr int PIECE_BYTES = 4096;   // unit of the all-gather pull: 32 lanes x 16 B x 8
+constexpr int RS_LAG = 4;          // reduce-scatter: own row block j is scheduled this many row blocks after the peers' j
 constexpr int FLAG_STRIDE = 32;     // u32 words between two ranks' "staged" flags (128 B)
 
 enum Mode : int32_t { MODE_PLAIN = 0, MODE_AG = 1, MODE_RS = 2 };
@@ -173,21 +174,50 @@ __device__ __forceinline__ TileInfo decode_tile(const KParams& p, const Sched& s
     ti.chunk = (p.mode == MODE_PLAIN) ? 0 : p.rank;
     ti.mt = t / s.nt_total;
     nt = t - ti.mt * s.nt_total;
-  } else {
-    const int remote_tiles = s.units_per_chunk * (p.ws - 1);
-    const bool own = (p.mode == MODE_AG) ? (t < s.units_per_chunk) : (t >= remote_tiles);
-    if (own) {
-      const int r = (p.mode == MODE_AG) ? t : t - remote_tiles;
+  } else if (p.mode == MODE_AG) {
+    if (t < s.units_per_chunk) {
       ti.chunk = p.rank;
-      ti.mt = r / s.nt_total;
-      nt = r - ti.mt * s.nt_total;
+      ti.mt = t / s.nt_total;
+      nt = t - ti.mt * s.nt_total;
     } else {
-      const int r = (p.mode == MODE_AG) ? t - s.units_per_chunk : t;
+      const int r = t - s.units_per_chunk;
       const int per_mt = s.nt_total * (p.ws - 1);
       ti.mt = r / per_mt;
       const int rr = r - ti.mt * per_mt;
       const int step = rr / s.nt_total;                 // 0 .. ws-2
       nt = rr - step * s.nt_total;
+      ti.chunk = (p.rank + 1 + step) % p.ws;
+    }
+  } else {
+    // Reduce-scatter: row block j of the local rank's chunk follows RS_LAG row blocks behind the
+    // peers' row block j (whose partials for it are then on their way or already here), so the
+    // NVLink traffic is spread over the whole kernel instead of stopping when the own chunk starts.
+    const int U = s.nt_total;                    // units per row block of one chunk
+    const int R = U * (p.ws - 1);                // remote units per row block
+    const int rows = s.units_per_chunk / U;      // row blocks (or pairs of them)
+    const int lag = rows < RS_LAG ? rows : RS_LAG;
+    const int head = lag * R;
+    const int body = (rows - lag) * (R + U);
+    int remote_r = -1, own_r = -1;               // index inside the remote / own sequence
+    if (t < head) {
+      remote_r = t;
+    } else if (t < head + body) {
+      const int t2 = t - head;
+      const int g = t2 / (R + U);
+      const int w = t2 - g * (R + U);
+      if (w < R) remote_r = (lag + g) * R + w; else own_r = g * U + (w - R);
+    } else {
+      own_r = (rows - lag) * U + (t - head - body);
+    }
+    if (own_r >= 0) {
+      ti.chunk = p.rank;
+      ti.mt = own_r / U;
+      nt = own_r - ti.mt * U;
+    } else {
+      ti.mt = remote_r / R;
+      const int rr = remote_r - ti.mt * R;
+      const int step = rr / U;                          // 0 .. ws-2
+      nt = rr - step * U;
       ti.chunk = (p.rank + 1 + step) % p.ws;
     }
   }
@@ -883,12 +913,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       // still busy sending other ranks' tiles.
       const int cw = warp - (2 + EPI_WARPS);
       const size_t src_stride = (size_t)sched.tiles_per_chunk * (BN / 64) * 4 * (32 * ROW_BYTES);
-      const int remote_tiles = sched.units_per_chunk * (p.ws - 1);
       uint32_t done = 0;
       bool ok = true;
       for (int t = tile_first; t < sched.total_tiles && ok; t += tile_step) {
-        if (t < remote_tiles) continue;
         const TileInfo ti = decode_tile<BN, PAIR>(p, sched, t, crank);
+        if (ti.chunk != p.rank) continue;
         if (cw == 0) {
           if (lane == 0) {
             for (int src = 0; src < p.ws && ok; ++src) {
