@@ -302,7 +302,7 @@ def run_ours(args) -> None:
                             "bound": "tensor" if FLOPS_RS / NOMINAL_BF16 >= nv_bytes / NVLINK_BPS else "nvlink"},
                 "nvlink_bytes_per_gpu_per_op": nv_bytes,
             },
-            "roofline": {"bound": "tensor", "kernel": "gemm_fused_kernel<256,4,false> (all-gather mode)", "achieved": ag_tf,
+            "roofline": {"bound": "tensor", "kernel": _kernel_name(L), "achieved": ag_tf,
                          "peak": peak_tf, "unit": "TFLOP/s", "frac": ag_tf / peak_tf, "peak_kind": f"of {peak_kind} (sustained cuBLAS bf16)",
                          "frac_of_nominal_2250": ag_tf / 2250.0, "traffic": _traffic_ag_bytes()},
             "e2e": {"value": world * FLOPS_STEP / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
@@ -321,8 +321,14 @@ def run_ours(args) -> None:
 
 # DRAM bytes (read + write) of one all-gather-mode launch at this workload, from the ncu capture
 # summarised in profiles/ (8192-token capture scaled to 32768 tokens: A and outputs scale, B does not).
+def _kernel_name(L) -> str:
+    pair = L.apk_pair_launch_count() > 0
+    return ("gemm_fused_kernel<256,6,false,true> (CTA pairs, all-gather mode)" if pair
+            else "gemm_fused_kernel<256,4,false,false> (all-gather mode)")
+
+
 def _traffic_ag_bytes() -> float:
-    per_8192 = (98.43e6 - 29.36e6) + 40.32e6     # A read + outputs written, measured at 8192 tokens
+    per_8192 = (99.09e6 - 29.36e6) + 41.10e6     # A read + outputs written, measured at 8192 tokens
     return 29.36e6 + per_8192 * TOKENS / 8192.0   # + B (w1, w3), read once whatever the tokens
 
 
