@@ -104,6 +104,8 @@ class ApkAgGemmArgs(C.Structure):
         ("a_scale_mode", C.c_int32),
         ("A_scale", C.c_void_p),
         ("A_scale_gathered", C.c_void_p),
+        ("gather_k", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 
@@ -117,7 +119,7 @@ class ApkGemmRsArgs(C.Structure):
         ("lda", C.c_int64),
         ("B", ApkOperand),
         ("a_scale_mode", C.c_int32),
-        ("reserved", C.c_int32),
+        ("scatter_cols", C.c_int32),
         ("A_scale", C.c_void_p),
     ]
 

@@ -352,10 +352,7 @@ def _ag_gemm_native(
     if gather_dim < 0 or gather_dim >= A_shard.dim():
         raise ValueError("Invalid gather_dim")
     if gather_dim == A_shard.dim() - 1:
-        raise NotImplementedError(
-            "fused_all_gather_matmul along the last dim is not built yet; set "
-            "autoparallel.asynctp._ag_mm_last_dim_enabled = False so the pass does not emit it"
-        )
+        return _ag_gemm_last_dim_native(A_shard, Bs, A_scale, out_dtypes, group_name, return_A)
     if not 1 <= len(Bs) <= nat.APK_MAX_B:
         raise NotImplementedError(f"between 1 and {nat.APK_MAX_B} B operands are supported, got {len(Bs)}")
     group = c10d._resolve_process_group(group_name)
@@ -421,6 +418,63 @@ def _ag_gemm_native(
     return A_ret, [unflatten(o) for o in outs]
 
 
+def _ag_gemm_last_dim_native(
+    A_shard: torch.Tensor,
+    Bs: list[torch.Tensor],
+    A_scale: torch.Tensor | None,
+    out_dtypes: list[torch.dtype | None],
+    group_name: str,
+    return_A: bool,
+) -> tuple[torch.Tensor | None, list[torch.Tensor]]:
+    """Gather along the LAST dim: every rank holds a K-slice of A, so
+    ``cat(A_shards, -1) @ B == sum_r A_r @ B[r*K:(r+1)*K]``; the kernel accumulates the slices in
+    TMEM in the order they arrive (counterpart of _fused_all_gather_matmul_last_gather_dim_impl,
+    autoparallel/asynctp_ops.py:602-669)."""
+    if A_scale is not None:
+        raise NotImplementedError("scaled all-gather matmul along the last dim is not supported (the reference has none either)")
+    if not 1 <= len(Bs) <= nat.APK_MAX_B:
+        raise NotImplementedError(f"between 1 and {nat.APK_MAX_B} B operands are supported, got {len(Bs)}")
+    group = c10d._resolve_process_group(group_name)
+    world = group.size()
+    if A_shard.dtype != torch.bfloat16:
+        raise NotImplementedError(f"all-gather matmul along the last dim takes bfloat16 operands, got {A_shard.dtype}")
+    lead = list(A_shard.shape[:-1])
+    A2 = _aligned(A_shard.flatten(0, -2).contiguous())
+    rows, Kc = A2.shape
+    for B in Bs:
+        if B.dtype != A_shard.dtype:
+            raise ValueError(f"B dtype {B.dtype} differs from A dtype {A_shard.dtype}")
+        if B.shape[0] != Kc * world:
+            raise ValueError(f"B has {B.shape[0]} rows but the gathered A has {Kc * world} columns")
+    outs = [A2.new_empty((rows, B.shape[1]), dtype=od or B.dtype) for B, od in zip(Bs, out_dtypes)]
+    need_gathered = world > 1 or return_A
+    stacked = A2.new_empty((world * rows, Kc)) if need_gathered else None   # [world][rows][Kc]
+
+    wsp = symm.get_workspace(group_name, A2.device)
+    args = nat.ApkAgGemmArgs()
+    keep: list = [A2]
+    args.dtype = nat.APK_BF16
+    args.rows_per_rank = rows
+    args.K = Kc
+    args.nB = len(Bs)
+    args.A_shard = A2.data_ptr()
+    args.lda = Kc
+    args.A_gathered = stacked.data_ptr() if stacked is not None else None
+    args.return_A = 1 if return_A else 0
+    args.gather_k = 1
+    for i, (B, out) in enumerate(zip(Bs, outs)):
+        _fill_operand(args.Bs[i], keep, B, out, None, None, None)
+    L = nat.lib()
+    wsp.ensure(L.apk_ag_gemm_arena_bytes(C.byref(args), world), L.apk_ctrl_bytes(rows, world))
+    comm = wsp.next_comm()
+    nat.check(L.apk_ag_gemm(C.byref(comm), C.byref(args), _stream_ptr(A2.device)))
+    A_ret = None
+    if return_A:
+        # the reference returns cat(shards, -1) (asynctp_ops.py:663-667); here one strided copy
+        A_ret = stacked.view(world, rows, Kc).permute(1, 0, 2).reshape(*lead, world * Kc)
+    return A_ret, [o.view(*lead, o.shape[-1]) for o in outs]
+
+
 def _gemm_rs_native(
     A2: torch.Tensor,
     B: torch.Tensor,
@@ -431,8 +485,10 @@ def _gemm_rs_native(
     out_dtype: torch.dtype,
     reduce_op: str,
     group_name: str,
+    scatter_cols: bool = False,
 ) -> torch.Tensor:
-    """[M, K] @ [K, N] -> rows [rank*M/world, (rank+1)*M/world) reduced over the group."""
+    """[M, K] @ [K, N] reduced over the group; this rank keeps rows [rank*M/world, (rank+1)*M/world),
+    or with ``scatter_cols`` columns [rank*N/world, (rank+1)*N/world) of all rows."""
     group = c10d._resolve_process_group(group_name)
     world = group.size()
     dtype_code = _in_dtype_code(A2, "A")
@@ -441,10 +497,11 @@ def _gemm_rs_native(
     M, K = A2.shape
     if B.shape[0] != K:
         raise ValueError(f"B has {B.shape[0]} rows but A has {K} columns")
-    if M % world != 0:
+    if not scatter_cols and M % world != 0:
         raise ValueError(f"the scatter dimension ({M} rows after flattening) is not divisible by the group size {world}")
     A2 = _aligned(A2.contiguous())
-    out = A2.new_empty((M // world, B.shape[1]), dtype=out_dtype)
+    out_shape = (M, B.shape[1] // world) if scatter_cols else (M // world, B.shape[1])
+    out = A2.new_empty(out_shape, dtype=out_dtype)
     wsp = symm.get_workspace(group_name, A2.device)
     args = nat.ApkGemmRsArgs()
     keep: list = [A2]
@@ -454,6 +511,7 @@ def _gemm_rs_native(
     args.reduce_op = nat.APK_REDUCE_SUM if reduce_op == "sum" else nat.APK_REDUCE_AVG
     args.A = A2.data_ptr()
     args.lda = K
+    args.scatter_cols = 1 if scatter_cols else 0
     _fill_operand(args.B, keep, B, out, B_scale, bias, result_scale)
     if A_scale_rows is not None:
         s = A_scale_rows.to(torch.float32).contiguous().view(-1)
@@ -550,12 +608,13 @@ def _fused_matmul_reduce_scatter(
         if B.dim() != 2:
             raise ValueError("B must be a matrix")
         _check_reduce_op(reduce_op)
-        if scatter_dim == A.dim() - 1:
-            raise NotImplementedError(
-                "fused_matmul_reduce_scatter along the last dim is not built yet; set "
-                "autoparallel.asynctp._mm_rs_last_dim_enabled = False so the pass does not emit it"
-            )
         world = c10d._resolve_process_group(group_name).size()
+        if scatter_dim == A.dim() - 1:
+            # rank d receives columns [d*N/world, (d+1)*N/world) of all rows (asynctp_ops.py:1129-1157)
+            if B.shape[1] % world != 0:
+                raise ValueError(f"B has {B.shape[1]} columns, not divisible by the group size {world}")
+            out = _gemm_rs_native(A.flatten(0, -2), B, None, None, None, None, A.dtype, reduce_op, group_name, scatter_cols=True)
+            return out.view(*A.shape[:-1], B.shape[1] // world)
         fronted = A.movedim(scatter_dim, 0)
         lead = list(fronted.shape[:-1])
         if lead[0] % world != 0:

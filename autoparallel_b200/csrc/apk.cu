@@ -194,7 +194,11 @@ int launch(const apk::KParams& kp, int max_n, bool fp8, cudaStream_t stream) {
 
 uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
 
-int fill_operand(apk::KParams* kp, int b, const apk_operand& op, int dtype, int K, int bn, int64_t out_rows, const char* what) {
+int fill_operand(apk::KParams* kp, int b, const apk_operand& op_in, int dtype, int K, int bn, int64_t out_rows, const char* what,
+                 int b_cols_total = 0) {
+  // b_cols_total: columns of the B tensor when the op works on a column slice of it (op.N is the slice width)
+  apk_operand op = op_in;
+  const uint64_t b_cols = b_cols_total > 0 ? (uint64_t)b_cols_total : (uint64_t)op.N;
   if (op.B == nullptr || op.out == nullptr) return fail(APK_ERR_ARG, "%s: null B or out", what);
   if (op.N <= 0) return fail(APK_ERR_ARG, "%s: N must be positive", what);
   if (op.out_dtype != APK_BF16 && op.out_dtype != APK_F32) return fail(APK_ERR_ARG, "%s: out dtype must be bf16 or f32", what);
@@ -206,11 +210,11 @@ int fill_operand(apk::KParams* kp, int b, const apk_operand& op, int dtype, int 
   const int bke = dtype == APK_BF16 ? 64 : 128;
   int rc;
   if (op.n_major) {
-    rc = encode_2d(&kp->tmB[b], dtype, op.B, (uint64_t)op.N, (uint64_t)K, (uint64_t)op.ldb, bke, bke, what);
+    rc = encode_2d(&kp->tmB[b], dtype, op.B, b_cols, (uint64_t)K, (uint64_t)op.ldb, bke, bke, what);
   } else {
-    rc = encode_2d(&kp->tmB[b], dtype, op.B, (uint64_t)K, (uint64_t)op.N, (uint64_t)op.ldb, bke, bn, what);
+    rc = encode_2d(&kp->tmB[b], dtype, op.B, (uint64_t)K, b_cols, (uint64_t)op.ldb, bke, bn, what);
     if (rc == APK_OK && bn == 256)   // a CTA of a pair loads 128 of the tile's 256 columns
-      rc = encode_2d(&kp->tmBp[b], dtype, op.B, (uint64_t)K, (uint64_t)op.N, (uint64_t)op.ldb, bke, bn / 2, what);
+      rc = encode_2d(&kp->tmBp[b], dtype, op.B, (uint64_t)K, b_cols, (uint64_t)op.ldb, bke, bn / 2, what);
   }
   if (rc != APK_OK) return rc;
   kp->N[b] = op.N;
@@ -321,15 +325,16 @@ uint64_t apk_ag_gemm_arena_bytes(const apk_ag_gemm_args* a, int32_t world) {
 
 uint64_t apk_gemm_rs_arena_bytes(const apk_gemm_rs_args* a, int32_t world) {
   if (a == nullptr || world <= 1) return 0;
-  const uint64_t rows = (uint64_t)(a->M / world);
+  const uint64_t rows = a->scatter_cols ? (uint64_t)a->M : (uint64_t)(a->M / world);   // rows of one destination's part
+  const uint64_t width = a->scatter_cols ? (uint64_t)(a->B.N / world) : (uint64_t)a->B.N;
   const uint64_t mt = (rows + apk::BM - 1) / apk::BM;
   if (a->B.out_dtype == APK_F32) {
     // fp32 partials: row-major, one slot per source rank padded to whole 128-row tiles
-    return align_up((uint64_t)world * mt * apk::BM * (uint64_t)a->B.N * 4, 256);
+    return align_up((uint64_t)world * mt * apk::BM * width * 4, 256);
   }
   // bf16 partials: whole tiles, stored as contiguous 32 x 64 blocks
-  const uint64_t bn = a->B.N <= 128 ? 128 : 256;
-  const uint64_t nt = ((uint64_t)a->B.N + bn - 1) / bn;
+  const uint64_t bn = width <= 128 ? 128 : 256;
+  const uint64_t nt = (width + bn - 1) / bn;
   // one slot per source rank, plus the fp32 sums of the peers' partials (twice a slot)
   return (uint64_t)(world + 2) * mt * nt * apk::BM * bn * 2;
 }
@@ -368,6 +373,10 @@ int apk_ag_gemm(const apk_comm* comm, const apk_ag_gemm_args* a, void* stream_) 
   kp.nB = a->nB;
   kp.M = (int32_t)M;
   kp.K = a->K;
+  kp.ag_ksplit = a->gather_k ? 1 : 0;
+  if (a->gather_k && (a->dtype != APK_BF16 || a->a_scale_mode != APK_SCALE_NONE))
+    return fail(APK_ERR_ARG, "gather_k supports bf16 without scales only");
+  if (a->gather_k && (int64_t)a->K * ws > 0x7fffffffLL) return fail(APK_ERR_ARG, "K too large");
   kp.rows_per_rank = a->rows_per_rank;
   kp.elem_bytes = es;
   int max_n = 0;
@@ -381,7 +390,8 @@ int apk_ag_gemm(const apk_comm* comm, const apk_ag_gemm_args* a, void* stream_) 
     if (rc != APK_OK) return rc;
   }
   for (int b = 0; b < a->nB; ++b) {
-    rc = fill_operand(&kp, b, a->Bs[b], a->dtype, a->K, bn, M, "Bs[i]");
+    // K-split: B spans all ranks' K-slices and the outputs have the shard's rows only
+    rc = fill_operand(&kp, b, a->Bs[b], a->dtype, a->gather_k ? a->K * ws : a->K, bn, a->gather_k ? a->rows_per_rank : M, "Bs[i]");
     if (rc != APK_OK) return rc;
   }
   // A scale
@@ -447,7 +457,9 @@ int apk_gemm_rs(const apk_comm* comm, const apk_gemm_rs_args* a, void* stream_) 
   if (a->dtype != APK_BF16 && a->dtype != APK_E4M3) return fail(APK_ERR_ARG, "dtype must be bf16 or e4m3");
   const int ws = comm->world;
   if (a->M < 0 || a->K <= 0) return fail(APK_ERR_ARG, "bad shape");
-  if (a->M % ws != 0) return fail(APK_ERR_ARG, "M (%d) must be divisible by the group size (%d)", a->M, ws);
+  if (!a->scatter_cols && a->M % ws != 0) return fail(APK_ERR_ARG, "M (%d) must be divisible by the group size (%d)", a->M, ws);
+  if (a->scatter_cols && (a->B.N % ws != 0 || a->a_scale_mode != APK_SCALE_NONE || a->B.b_scale_mode != APK_SCALE_NONE))
+    return fail(APK_ERR_ARG, "scatter_cols needs N divisible by the group size and no scales");
   if (a->M == 0) return APK_OK;
   if (a->A == nullptr) return fail(APK_ERR_ARG, "A is null");
   if (a->reduce_op != APK_REDUCE_SUM && a->reduce_op != APK_REDUCE_AVG) return fail(APK_ERR_ARG, "reduce_op must be sum or avg");
@@ -465,14 +477,20 @@ int apk_gemm_rs(const apk_comm* comm, const apk_gemm_rs_args* a, void* stream_) 
   kp.nB = 1;
   kp.M = a->M;
   kp.K = a->K;
-  kp.rows_per_rank = a->M / ws;
+  kp.rs_colsplit = a->scatter_cols ? 1 : 0;
+  kp.rows_per_rank = a->scatter_cols ? a->M : a->M / ws;
+  const int width = a->scatter_cols ? a->B.N / ws : a->B.N;   // columns of one destination's part
   kp.rs_slot_rows = (int32_t)align_up((uint64_t)kp.rows_per_rank, apk::BM);
   kp.elem_bytes = es;
-  const int bn = a->B.N <= 128 ? 128 : 256;
+  const int bn = width <= 128 ? 128 : 256;
   const int bke = a->dtype == APK_BF16 ? 64 : 128;
   rc = encode_2d(&kp.tmA0, a->dtype, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, bke, apk::BM, "A");
   if (rc != APK_OK) return rc;
-  rc = fill_operand(&kp, 0, a->B, a->dtype, a->K, bn, a->M / ws, "B");
+  {
+    apk_operand opB = a->B;
+    opB.N = width;
+    rc = fill_operand(&kp, 0, opB, a->dtype, a->K, bn, kp.rows_per_rank, "B", a->B.N);
+  }
   if (rc != APK_OK) return rc;
   switch (a->a_scale_mode) {
     case APK_SCALE_NONE:
@@ -499,7 +517,7 @@ int apk_gemm_rs(const apk_comm* comm, const apk_gemm_rs_args* a, void* stream_) 
     const uint64_t need = apk_gemm_rs_arena_bytes(a, ws);
     if (need > half) return fail(APK_ERR_SIZE, "reduce-scatter arena needs %llu bytes per half, arena has %llu", (unsigned long long)need, (unsigned long long)half);
     const uint64_t max_tiles = (comm->flag_bytes - kFlagRsOffset) / 4 / (uint64_t)ws;
-    const uint64_t tiles = (uint64_t)((kp.rows_per_rank + apk::BM - 1) / apk::BM) * (uint64_t)((a->B.N + bn - 1) / bn);
+    const uint64_t tiles = (uint64_t)((kp.rows_per_rank + apk::BM - 1) / apk::BM) * (uint64_t)((width + bn - 1) / bn);
     if (tiles > max_tiles) return fail(APK_ERR_SIZE, "signal pad holds %llu tile flags per rank, need %llu", (unsigned long long)max_tiles, (unsigned long long)tiles);
     kp.rs_max_tiles = (int32_t)max_tiles;
     kp.rs_slot_rows = (int32_t)align_up((uint64_t)kp.rows_per_rank, apk::BM);
@@ -514,7 +532,7 @@ int apk_gemm_rs(const apk_comm* comm, const apk_gemm_rs_args* a, void* stream_) 
     kp.rs_sum_local = reinterpret_cast<float*>(kp.rs_arena_local + (uint64_t)ws * tiles * apk::BM * bn * 2);
     kp.rs_flag_local = kp.rs_flag_peer[comm->rank];
   }
-  return launch(kp, a->B.N, a->dtype == APK_E4M3, stream);
+  return launch(kp, width, a->dtype == APK_E4M3, stream);
 }
 
 int apk_check_status(const apk_comm* comm, void* stream_, uint32_t* raw) {

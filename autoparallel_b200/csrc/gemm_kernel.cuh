@@ -62,6 +62,8 @@ struct alignas(64) KParams {
   CUtensorMap tmOut[MAX_B];            // bf16 outputs, box 32 rows x 64 columns (TMA stores)
   int32_t mode, ws, rank, nB;
   int32_t M, K, rows_per_rank, elem_bytes;
+  int32_t ag_ksplit;           // AG along the LAST dim: shards are K-slices [rows, K]; out = sum_r A_r @ B[r*K:(r+1)*K]
+  int32_t rs_colsplit;         // RS along the LAST dim: rank d receives columns [d*N, (d+1)*N) of all rows
   int32_t N[MAX_B];
   int32_t b_nmajor[MAX_B];     // 1: B is [K][N] with N contiguous; 0: K contiguous
   void* out[MAX_B];
@@ -154,7 +156,7 @@ __device__ __forceinline__ Sched make_sched(const KParams& p) {
   s.mt_per_chunk = (p.rows_per_rank + BM - 1) / BM;
   s.tiles_per_chunk = s.mt_per_chunk * s.nt_total;
   s.units_per_chunk = (PAIR ? s.mt_per_chunk / 2 : s.mt_per_chunk) * s.nt_total;
-  s.num_chunks = (p.mode == MODE_PLAIN) ? 1 : p.ws;
+  s.num_chunks = (p.mode == MODE_PLAIN || p.ag_ksplit) ? 1 : p.ws;
   s.total_tiles = s.units_per_chunk * s.num_chunks;
   return s;
 }
@@ -170,8 +172,8 @@ template <int BN, bool PAIR = false>
 __device__ __forceinline__ TileInfo decode_tile(const KParams& p, const Sched& s, int t, int crank = 0) {
   TileInfo ti;
   int nt;
-  if (p.mode == MODE_PLAIN || p.ws == 1) {
-    ti.chunk = (p.mode == MODE_PLAIN) ? 0 : p.rank;
+  if (p.mode == MODE_PLAIN || p.ws == 1 || p.ag_ksplit) {
+    ti.chunk = (p.mode == MODE_PLAIN || p.ag_ksplit) ? 0 : p.rank;
     ti.mt = t / s.nt_total;
     nt = t - ti.mt * s.nt_total;
   } else if (p.mode == MODE_AG) {
@@ -430,7 +432,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
   const int crank = PAIR ? (int)ptx::cluster_ctarank() : 0;          // rank inside the pair
   const int tile_first = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int tile_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
-  const int num_kb = (p.K + BKE - 1) / BKE;
+  const int kb_per_shard = (p.K + BKE - 1) / BKE;
+  const int num_kb = p.ag_ksplit ? kb_per_shard * p.ws : kb_per_shard;   // K-split: every rank's K-slice in turn
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -472,7 +475,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
         const TileInfo ti = decode_tile<BN, PAIR>(p, sched, t, crank);
         const CUtensorMap* tmA = &p.tmA0;
         int arow = ti.mt * BM;
-        if (p.mode == MODE_AG && ti.chunk != p.rank) {
+        int bcol = ti.n0;     // first column of B for this tile
+        if (p.ag_ksplit) {
+          // handled per k-block below: the source rank changes along K
+        } else if (p.mode == MODE_AG && ti.chunk != p.rank) {
           tmA = &p.tmA1;
           arow += ti.chunk * p.rows_per_rank;
           const uint32_t expect = (uint32_t)ag_tile_pieces(p, ti.mt) + (p.ag_has_scale ? 1u : 0u);
@@ -481,13 +487,32 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
           if (!ok) break;
           ptx::fence_proxy_async_global();
         } else if (p.mode == MODE_RS) {
-          arow += ti.chunk * p.rows_per_rank;
+          if (p.rs_colsplit) bcol += ti.chunk * p.N[0]; else arow += ti.chunk * p.rows_per_rank;
         }
         const bool nmajor = p.b_nmajor[ti.b] != 0;
         const CUtensorMap* tmB = &p.tmB[ti.b];
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
+          int ka = kb * BKE, kbB = kb * BKE;     // K coordinates in A and in B
+          if (p.ag_ksplit) {
+            // K-slice of rank (rank + step): own slice first, then the peers' as they arrive
+            const int step = kb / kb_per_shard;
+            const int src = (p.rank + step) % p.ws;
+            ka = (kb - step * kb_per_shard) * BKE;
+            kbB = src * p.K + ka;
+            if (ka == 0) {
+              tmA = (src == p.rank) ? &p.tmA0 : &p.tmA1;
+              arow = ti.mt * BM + ((src == p.rank) ? 0 : src * p.rows_per_rank);
+              if (src != p.rank) {
+                const uint32_t expect = (uint32_t)ag_tile_pieces(p, ti.mt);
+                ok = flag_wait<false>(p.ready + src * sched.mt_per_chunk + ti.mt, expect, p, abort_flag,
+                                      ST_TIMEOUT_READY, (uint32_t)src);
+                if (!ok) break;
+                ptx::fence_proxy_async_global();
+              }
+            }
+          }
           ok = mbar_wait(empty_bar(s), ph ^ 1u, p, abort_flag);
           if (!ok) break;
           const uint32_t a_dst = smem_base + s * L::STAGE_BYTES;
@@ -495,26 +520,26 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
           if (PAIR) {
             // this CTA's A rows and its half of B's columns; bytes are counted on rank 0's barrier
             const uint32_t fb = ptx::mapa(full_bar(s), 0);
-            const int nb = ti.n0 + crank * (BN / 2);
+            const int nb = bcol + crank * (BN / 2);
             ptx::mbar_expect_tx_cluster(fb, L::STAGE_BYTES);
-            ptx::tma_load_2d_pair(a_dst, tmA, fb, kb * BKE, arow);
+            ptx::tma_load_2d_pair(a_dst, tmA, fb, ka, arow);
             if (!nmajor) {
-              ptx::tma_load_2d_pair(b_dst, &p.tmBp[ti.b], fb, kb * BKE, nb);
+              ptx::tma_load_2d_pair(b_dst, &p.tmBp[ti.b], fb, kbB, nb);
             } else {
 #pragma unroll
               for (int j = 0; j < BN / 2 / NPB; ++j) {
-                ptx::tma_load_2d_pair(b_dst + j * (BKE * ROW_BYTES), tmB, fb, nb + j * NPB, kb * BKE);
+                ptx::tma_load_2d_pair(b_dst + j * (BKE * ROW_BYTES), tmB, fb, nb + j * NPB, kbB);
               }
             }
           } else {
             ptx::mbar_expect_tx(full_bar(s), L::STAGE_BYTES);
-            ptx::tma_load_2d(a_dst, tmA, full_bar(s), kb * BKE, arow);
+            ptx::tma_load_2d(a_dst, tmA, full_bar(s), ka, arow);
             if (!nmajor) {
-              ptx::tma_load_2d(b_dst, tmB, full_bar(s), kb * BKE, ti.n0);
+              ptx::tma_load_2d(b_dst, tmB, full_bar(s), kbB, bcol);
             } else {
 #pragma unroll
               for (int j = 0; j < BN / NPB; ++j) {
-                ptx::tma_load_2d(b_dst + j * (BKE * ROW_BYTES), tmB, full_bar(s), ti.n0 + j * NPB, kb * BKE);
+                ptx::tma_load_2d(b_dst + j * (BKE * ROW_BYTES), tmB, full_bar(s), bcol + j * NPB, kbB);
               }
             }
           }
@@ -664,7 +689,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       const uint32_t aph = (lt >> 1) & 1u;
       const bool row_ok = row_in_tile < ti.rows_valid;
       const int chunk_row = ti.mt * BM + row_in_tile;                   // row inside the chunk
-      const long long grow = (long long)ti.chunk * p.rows_per_rank + chunk_row;  // row of the full matrix
+      const long long grow = (p.rs_colsplit ? 0LL : (long long)ti.chunk * p.rows_per_rank) + chunk_row;  // row of the full matrix
       const int b = ti.b;
       const bool own = (p.mode != MODE_RS) || (ti.chunk == p.rank);
 

@@ -118,6 +118,11 @@ typedef struct {
   int32_t a_scale_mode;   /* NONE / SCALAR / VECTOR (row-wise, sharded like A) / ROWS_REPLICATED */
   const float* A_scale;
   float* A_scale_gathered; /* [world*rows_per_rank] scratch, required for VECTOR when world > 1 */
+  int32_t gather_k;       /* 0: shards are row blocks of A (rows ordered by rank). 1: shards are K-slices
+                             [rows_per_rank, K] of A [rows_per_rank, world*K]; every B is [world*K, N],
+                             outs[b] is [rows_per_rank, N], A_gathered is [world][rows_per_rank][K]
+                             (autoparallel/asynctp_ops.py:602-669). bf16, no scales. */
+  int32_t reserved;
 } apk_ag_gemm_args;
 
 /*
@@ -134,7 +139,9 @@ typedef struct {
   int64_t lda;
   apk_operand B;          /* B.out is [M/world, N] */
   int32_t a_scale_mode;   /* NONE / SCALAR / VECTOR (one per row of A) */
-  int32_t reserved;
+  int32_t scatter_cols;   /* 0: rank d receives rows [d*M/world, ...). 1: rank d receives columns
+                             [d*N/world, ...) of all M rows: B.N is the FULL width, B.out is [M, N/world]
+                             (autoparallel/asynctp_ops.py:1129-1157). No scales. */
   const float* A_scale;
 } apk_gemm_rs_args;
 

@@ -39,7 +39,7 @@ def test_struct_layouts_match_header():
     # sizes the C compiler gives the structs in include/apk.h (LP64)
     assert C.sizeof(nat.ApkComm) == 8 + 8 * 8 + 8 * 8 + 8 + 8 + 8 + 8 + 8 + 4 + 4 + 8
     assert C.sizeof(nat.ApkOperand) == 80
-    assert C.sizeof(nat.ApkAgGemmArgs) == 16 + 8 + 8 + 4 * 80 + 8 + 8 + 8 + 8
+    assert C.sizeof(nat.ApkAgGemmArgs) == 16 + 8 + 8 + 4 * 80 + 8 + 8 + 8 + 8 + 8
     assert C.sizeof(nat.ApkGemmRsArgs) == 16 + 8 + 8 + 80 + 8 + 8
 
 

@@ -94,6 +94,52 @@ def test_all_gather_matmul_nd_and_return_A(group):
     assert orc.rel_fro_error(outs[0], outs_ref[0].double()) <= BF16_TOL
 
 
+def test_last_dim_variants_single_rank(group):
+    """Gather / scatter along the last dim with a group of one: the K-split and column-split paths."""
+    orc = _orc()
+    A = orc.activations(4, 6 * 50, 192).view(6, 50, 192)
+    Bs = [orc.weights(7, 192, 264), orc.weights(8, 192, 128)]
+    A_out, outs = _ag(A, Bs, 2, group, True)
+    A_ref, outs_ref = orc.all_gather_matmul_local([A], Bs, 2, True)
+    assert torch.equal(A_out.cpu(), A_ref)
+    for o, o_ref, b in zip(outs, outs_ref, Bs):
+        assert o.shape == o_ref.shape and orc.rel_fro_error(o, A.double() @ b.double()) <= BF16_TOL
+    out = torch.ops._ap_symm_mem.fused_matmul_reduce_scatter(A.cuda(), Bs[0].cuda(), "sum", 2, group)
+    (ref,) = orc.matmul_reduce_scatter_local([A], [Bs[0]], "sum", 2)
+    assert out.shape == ref.shape and orc.rel_fro_error(out, A.double() @ Bs[0].double()) <= BF16_TOL
+
+
+def test_all_gather_last_dim_receive_side_on_one_gpu(group):
+    """Rank 0 of a two-rank all-gather along the LAST dim on a single GPU (the peer's K-slice is staged
+    beforehand): out = A_0 @ B[:K] + A_1 @ B[K:], accumulated in TMEM in arrival order."""
+    from autoparallel_b200 import _native as nat
+    from tests.test_zz_no_alloc import _TwoRankHarness
+
+    L = nat.lib()
+    orc = _orc()
+    rows, Kc, N = 384, 256, 264
+    h = _TwoRankHarness(nat, rows, Kc, False)
+    B = orc.weights(7, 2 * Kc, N).cuda()
+    ref64 = torch.cat([s.cpu().double() for s in h.shards], dim=1) @ B.cpu().double()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for epoch in (1, 2):
+        out = torch.full((rows, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        stacked = torch.empty(2 * rows, Kc, dtype=torch.bfloat16, device="cuda")
+        c = h.comm(epoch, with_ctrl=True)
+        a = nat.ApkAgGemmArgs()
+        a.dtype, a.rows_per_rank, a.K, a.nB, a.gather_k = nat.APK_BF16, rows, Kc, 1, 1
+        a.A_shard, a.lda = h.shards[0].data_ptr(), Kc
+        a.A_gathered, a.return_A = stacked.data_ptr(), 1
+        op = a.Bs[0]
+        op.B, op.ldb, op.n_major, op.N = B.data_ptr(), N, 1, N
+        op.out, op.ldo, op.out_dtype = out.data_ptr(), N, nat.APK_BF16
+        assert L.apk_ag_gemm(C.byref(c), C.byref(a), stream) == nat.APK_OK, L.apk_last_error()
+        raw = C.c_uint32(0)
+        assert L.apk_check_status(C.byref(c), stream, C.byref(raw)) == nat.APK_OK, L.apk_last_error()
+        assert orc.rel_fro_error(out, ref64) <= BF16_TOL
+        assert torch.equal(stacked[:rows], h.shards[0]) and torch.equal(stacked[rows:], h.shards[1])
+
+
 def test_golden_all_gather_matmul(group, golden):
     """bf16 golden cases: the gathered A the reference produced, times the Bs, must give its outputs."""
     orc = _orc()

@@ -114,7 +114,7 @@ def test_argument_errors_match_reference(fake_pg):
         ops._ag_gemm_native(A, [B], None, n, n, n, [bf], 2, g, True)
     with pytest.raises(ValueError, match="len\\(out_types\\)"):
         ops._ag_gemm_native(A, [B], None, n, n, n, [], 0, g, True)
-    with pytest.raises(NotImplementedError, match="last dim"):
+    with pytest.raises(ValueError, match="gathered A has 512 columns"):   # last-dim gather: B must span all K-slices
         ops._ag_gemm_native(A, [B], None, n, n, n, [bf], 1, g, True)
     with pytest.raises(NotImplementedError, match="bfloat16 or float8_e4m3fn"):
         ops._ag_gemm_native(A.float(), [B.float()], None, n, n, n, [torch.float32], 0, g, True)
