@@ -52,48 +52,66 @@ def _peaks():
     return 1400.0, "fallback"
 
 
+_SAMPLER_CHILD = r"""
+import sys, time
+import pynvml
+pynvml.nvmlInit()
+h = pynvml.nvmlDeviceGetHandleByIndex(int(sys.argv[1]))
+print("max", pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM), flush=True)
+while True:
+    try:
+        bits = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+    except AttributeError:
+        bits = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+    print(time.time_ns(), pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM), int(bits), flush=True)
+    time.sleep(0.001)
+"""
+
+
 class ClockSampler:
-    """SM clock and clock-event (throttle) reasons of one GPU, polled through NVML every few
-    milliseconds by a thread while the timed region runs. Read-only."""
+    """SM clock and clock-event (throttle) reasons of one GPU, polled through NVML about every
+    millisecond by a child process (so that this process's Python threads cannot starve it);
+    `stop(t0, t1)` keeps the samples taken between two host timestamps. Read-only."""
 
     REASONS = {  # nvmlClocksEventReasons bits
         0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
     }
 
     def __init__(self, index: int):
-        import threading
-
-        self.index, self.sm, self.bits, self.max_mhz, self.err = index, [], 0, None, None
-        self._stop = threading.Event()
-        self._thread = threading.Thread(target=self._run, daemon=True)
-
-    def _run(self):
-        try:
-            import pynvml
-
-            pynvml.nvmlInit()
-            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
-            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
-            while not self._stop.is_set():
-                self.sm.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
-                try:
-                    self.bits |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
-                except AttributeError:
-                    self.bits |= int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
-                time.sleep(0.002)
-        except Exception as e:  # NVML missing: report it instead of failing the benchmark
-            self.err = repr(e)
+        self.index, self.proc, self.path = index, None, None
 
     def start(self):
-        self._thread.start()
+        import subprocess
 
-    def stop(self) -> dict:
-        self._stop.set()
-        self._thread.join(timeout=5)
-        if self.err or not self.sm:
-            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "samples": 0, "reasons": [f"nvml unavailable: {self.err}"]}
-        return {"sm_mhz": statistics.median(self.sm), "sm_max_mhz": self.max_mhz, "samples": len(self.sm),
-                "reasons": sorted(n for b, n in self.REASONS.items() if self.bits & b)}
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".txt", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen([sys.executable, "-c", _SAMPLER_CHILD, str(self.index)], stdout=f,
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self, t0_ns: int, t1_ns: int) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["nvml sampler could not start"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, bits, mx = [], 0, None
+        for line in Path(self.path).read_text().splitlines():
+            c = line.split()
+            if len(c) == 2 and c[0] == "max":
+                mx = float(c[1])
+            elif len(c) == 3 and t0_ns <= int(c[0]) <= t1_ns:
+                sm.append(float(c[1]))
+                bits |= int(c[2])
+        os.unlink(self.path)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": mx, "samples": 0, "reasons": ["no NVML sample inside the timed region"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": mx, "samples": len(sm),
+                "reasons": sorted(n for b, n in self.REASONS.items() if bits & b)}
 
 
 # ------------------------------------------------------------------------------------------ CPU arms
@@ -200,6 +218,9 @@ def run_ours(args) -> None:
     import autoparallel_b200.asynctp_ops  # noqa: F401
     from oracle import asynctp_oracle as orc  # input generators only; nothing computes through it here
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()          # polls from now on; only the samples inside the timed region are kept
     build_native()
     L = nat.lib()
     ns = torch.ops._ap_symm_mem
@@ -238,11 +259,9 @@ def run_ours(args) -> None:
 
     # ---- timed region: K steps, device-resident inputs; per-op events ride along on the same stream
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     launches0 = L.apk_launch_count()
     sync_all()
+    t0_ns = time.time_ns()
     t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_begin.record()
     for i in range(K):
@@ -253,30 +272,55 @@ def run_ours(args) -> None:
         ev[i][2].record()
     t_end.record()
     sync_all()
+    t1_ns = time.time_ns()
     launches = L.apk_launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t0_ns, t1_ns) if rank == 0 else None
     ms_step = max_over_ranks(t_begin.elapsed_time(t_end) / K)
     ms_ag = max_over_ranks(statistics.mean(e[0].elapsed_time(e[1]) for e in ev))
     ms_rs = max_over_ranks(statistics.mean(e[1].elapsed_time(e[2]) for e in ev))
     symm.sync_check()
 
-    # ---- end to end: host input -> device, both ops with the real silu*mul between them, result -> host
+    # ---- end to end: every step copies its input from pinned host memory, runs both ops with the real
+    #      silu*mul between them and copies the result back to pinned host memory. The copies run on
+    #      their own streams, double-buffered, so the copy of step i+1 overlaps the compute of step i
+    #      (what a caller feeding the op from host memory would do); the timed region ends when the last
+    #      result has landed on the host.
     out_host = torch.empty(rows, HIDDEN, dtype=torch.bfloat16).pin_memory()
+    main = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    x_dev = [torch.empty_like(x), torch.empty_like(x)]
+    ev_in = [torch.cuda.Event(), torch.cuda.Event()]
+    ev_free = [torch.cuda.Event(), torch.cuda.Event()]
+    for e in ev_free:
+        e.record(main)
 
-    def e2e_step():
-        xd = x_host.to(dev, non_blocking=True)
-        _, (a, b) = ns.fused_all_gather_matmul(xd, [w1, w3], 0, g, return_A=False)
-        hh = torch.nn.functional.silu(a).mul_(b)
+    def e2e_step(i: int):
+        b = i & 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_free[b])            # the compute that last read this buffer is done
+            x_dev[b].copy_(x_host, non_blocking=True)
+            ev_in[b].record(s_in)
+        main.wait_event(ev_in[b])
+        _, (a, bb) = ns.fused_all_gather_matmul(x_dev[b], [w1, w3], 0, g, return_A=False)
+        ev_free[b].record(main)
+        hh = torch.nn.functional.silu(a).mul_(bb)
         o = ns.fused_matmul_reduce_scatter(hh, w2, "sum", 0, g)
-        out_host.copy_(o, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record(main)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(done)
+            out_host.copy_(o, non_blocking=True)
+        o.record_stream(s_out)
 
-    for _ in range(3):
-        e2e_step()
+    for i in range(4):
+        e2e_step(i)
+    main.wait_stream(s_out)
     sync_all()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(K):
-        e2e_step()
+    for i in range(K):
+        e2e_step(i)
+    main.wait_stream(s_out)
     e1.record()
     sync_all()
     ms_e2e = max_over_ranks(e0.elapsed_time(e1) / K)
