@@ -376,15 +376,14 @@ __device__ __forceinline__ void add_row32(const void* src, float (&v)[32], int n
   }
 }
 
-// One warp copies up to 4 KiB (n16 16-byte words) src -> dst (and dst2 when given).
-template <bool PEER>
+// One warp copies up to 4 KiB (n16 16-byte words) of local memory src -> dst (and dst2 when given).
 __device__ __forceinline__ void copy_piece(const uint8_t* src, uint8_t* dst, uint8_t* dst2, int n16, int lane) {
   uint4 r[8];
 #pragma unroll
   for (int u = 0; u < 8; ++u) {
     const int i = u * 32 + lane;
     if (i < n16) {
-      r[u] = PEER ? ptx::ld_relaxed_sys_v4(src + (size_t)i * 16) : __ldcg(reinterpret_cast<const uint4*>(src) + i);
+      r[u] = __ldcg(reinterpret_cast<const uint4*>(src) + i);
     }
   }
 #pragma unroll
@@ -1015,7 +1014,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
         for (int q = gw; q < total_pieces; q += total_warps) {
           const long long off = (long long)q * PIECE_BYTES;
           const int n16 = (int)(min((long long)PIECE_BYTES, p.ag_chunk_bytes - off) >> 4);
-          copy_piece<false>(p.ag_src + off, dst_a + off, dst_b ? dst_b + off : nullptr, n16, lane);
+          copy_piece(p.ag_src + off, dst_a + off, dst_b ? dst_b + off : nullptr, n16, lane);
         }
         if (p.ag_has_scale && stage_symm) {
           float* sdst = reinterpret_cast<float*>(p.ag_symm_local + p.ag_scale_off);
