@@ -49,6 +49,8 @@ EXPORTED_SYMBOLS = (
     "apk_ag_gemm",
     "apk_gemm_rs",
     "apk_ag_gemm_static",
+    "apk_all_gather",
+    "apk_reduce_scatter",
     "apk_check_status",
     "apk_launch_count",
     "apk_pair_launch_count",
@@ -162,6 +164,10 @@ def lib() -> C.CDLL:
     L.apk_gemm_rs.argtypes = [C.POINTER(ApkComm), C.POINTER(ApkGemmRsArgs), C.c_void_p]
     L.apk_ag_gemm_static.argtypes = [C.POINTER(ApkComm), C.POINTER(ApkAgGemmArgs), C.c_void_p]
     L.apk_ag_gemm_static.restype = C.c_int
+    L.apk_all_gather.argtypes = [C.POINTER(ApkComm), C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]
+    L.apk_all_gather.restype = C.c_int
+    L.apk_reduce_scatter.argtypes = [C.POINTER(ApkComm), C.c_void_p, C.c_void_p, C.c_uint64, C.c_int32, C.c_int32, C.c_void_p]
+    L.apk_reduce_scatter.restype = C.c_int
     L.apk_check_status.argtypes = [C.POINTER(ApkComm), C.c_void_p, C.POINTER(C.c_uint32)]
     L.apk_launch_count.restype = C.c_uint64
     L.apk_pair_launch_count.restype = C.c_uint64

@@ -701,15 +701,38 @@ def _low_contention_reduce_scatter_meta(tensor: torch.Tensor, reduce_op: str, gr
 
 @torch.library.impl(lib, "_low_contention_all_gather", "CUDA")
 def _low_contention_all_gather(tensor: torch.Tensor, group_name: str) -> torch.Tensor:
-    raise NotImplementedError(
-        "_low_contention_all_gather has no caller in AutoParallel (autoparallel/asynctp_ops.py:1524-1610) "
-        "and is not built; use funcol.all_gather_tensor"
-    )
+    """``all_gather_tensor(tensor, 0, group_name)`` as one copy kernel over the NVLink peer mappings
+    (counterpart of autoparallel/asynctp_ops.py:1524-1610; any dtype, the shard's bytes must be a
+    multiple of 16)."""
+    world = c10d._resolve_process_group(group_name).size()
+    x = _aligned(tensor.contiguous())
+    out = x.new_empty((x.shape[0] * world, *x.shape[1:]))
+    nbytes = x.numel() * x.element_size()
+    wsp = symm.get_workspace(group_name, x.device)
+    wsp.ensure(nbytes if world > 1 else 0, 256)
+    comm = wsp.next_comm()
+    nat.check(nat.lib().apk_all_gather(C.byref(comm), C.c_void_p(x.data_ptr()), C.c_void_p(out.data_ptr()), nbytes, _stream_ptr(x.device)))
+    return out
 
 
 @torch.library.impl(lib, "_low_contention_reduce_scatter", "CUDA")
 def _low_contention_reduce_scatter(tensor: torch.Tensor, reduce_op: str, group_name: str) -> torch.Tensor:
-    raise NotImplementedError(
-        "_low_contention_reduce_scatter has no caller in AutoParallel (autoparallel/asynctp_ops.py:1613-1702) "
-        "and is not built; use funcol.reduce_scatter_tensor"
-    )
+    """``reduce_scatter_tensor(tensor, reduce_op, 0, group_name)`` with the parts stored straight into
+    the owning peers' arenas and summed in fp32 there (counterpart of
+    autoparallel/asynctp_ops.py:1613-1702; bfloat16 or float32)."""
+    _check_reduce_op(reduce_op)
+    world = c10d._resolve_process_group(group_name).size()
+    if tensor.dtype not in (torch.bfloat16, torch.float32):
+        raise NotImplementedError(f"_low_contention_reduce_scatter takes bfloat16 or float32, got {tensor.dtype}")
+    if tensor.shape[0] % world != 0:
+        raise ValueError(f"dim 0 ({tensor.shape[0]}) is not divisible by the group size {world}")
+    x = _aligned(tensor.contiguous())
+    out = x.new_empty((x.shape[0] // world, *x.shape[1:]))
+    nbytes = out.numel() * out.element_size()
+    wsp = symm.get_workspace(group_name, x.device)
+    wsp.ensure(nbytes * world if world > 1 else 0, 256)
+    comm = wsp.next_comm()
+    nat.check(nat.lib().apk_reduce_scatter(
+        C.byref(comm), C.c_void_p(x.data_ptr()), C.c_void_p(out.data_ptr()), nbytes, _DTYPE_CODE[x.dtype],
+        nat.APK_REDUCE_SUM if reduce_op == "sum" else nat.APK_REDUCE_AVG, _stream_ptr(x.device)))
+    return out

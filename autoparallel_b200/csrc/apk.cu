@@ -13,6 +13,7 @@
 
 #include "../../include/apk.h"
 #include "gemm_kernel.cuh"
+#include "collectives_kernel.cuh"
 
 namespace {
 
@@ -533,6 +534,84 @@ int apk_gemm_rs(const apk_comm* comm, const apk_gemm_rs_args* a, void* stream_) 
     kp.rs_flag_local = kp.rs_flag_peer[comm->rank];
   }
   return launch(kp, width, a->dtype == APK_E4M3, stream);
+}
+
+// ---- stand-alone collectives over the same arena / flags / epoch protocol
+static int coll_common(const apk_comm* comm, uint64_t chunk_bytes, uint64_t arena_need, apk::CParams* cp, cudaStream_t stream) {
+  int rc = check_comm(comm);
+  if (rc != APK_OK) return rc;
+  if (chunk_bytes % 16 != 0) return fail(APK_ERR_ARG, "every rank's part (%llu bytes) must be a multiple of 16 bytes", (unsigned long long)chunk_bytes);
+  DeviceInfo di;
+  rc = device_info(&di);
+  if (rc != APK_OK) return rc;
+  memset(cp, 0, sizeof(*cp));
+  cp->ws = comm->world;
+  cp->rank = comm->rank;
+  cp->epoch = comm->epoch;
+  cp->chunk_bytes = (long long)chunk_bytes;
+  cp->status = comm->status;
+  cp->timeout_cycles = timeout_cycles(comm, di);
+  cp->reduce_scale = 1.0f;
+  if (comm->world > 1) {
+    const uint64_t half = comm->data_bytes / 2;
+    if (arena_need > half) return fail(APK_ERR_SIZE, "collective needs %llu bytes per arena half, arena has %llu", (unsigned long long)arena_need, (unsigned long long)half);
+    const uint64_t off = (comm->epoch & 1u) ? half : 0;
+    for (int r = 0; r < comm->world; ++r) cp->symm_peer[r] = reinterpret_cast<uint8_t*>(comm->data[r]) + off;
+    cp->symm_local = cp->symm_peer[comm->rank];
+    cp->ctrl = reinterpret_cast<uint32_t*>(comm->ctrl);
+    APK_CUDA(cudaMemsetAsync(comm->ctrl, 0, 256, stream));
+  }
+  return APK_OK;
+}
+
+int apk_all_gather(const apk_comm* comm, const void* shard, void* out, uint64_t shard_bytes, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (shard_bytes == 0) return APK_OK;
+  if (shard == nullptr || out == nullptr) return fail(APK_ERR_ARG, "null buffer");
+  if (((reinterpret_cast<uintptr_t>(shard) | reinterpret_cast<uintptr_t>(out)) & 15u) != 0) return fail(APK_ERR_ARG, "buffers must be 16-byte aligned");
+  apk::CParams cp;
+  int rc = coll_common(comm, shard_bytes, shard_bytes, &cp, stream);
+  if (rc != APK_OK) return rc;
+  cp.src = reinterpret_cast<const uint8_t*>(shard);
+  cp.out = reinterpret_cast<uint8_t*>(out);
+  cp.flag_stride = apk::FLAG_STRIDE;
+  for (int r = 0; r < comm->world && comm->world > 1; ++r) cp.flag_peer[r] = reinterpret_cast<uint32_t*>(comm->flags[r]);
+  cp.flag_local = comm->world > 1 ? cp.flag_peer[comm->rank] : nullptr;
+  DeviceInfo di;
+  device_info(&di);
+  apk::all_gather_kernel<<<di.sms, apk::COLL_THREADS, 0, stream>>>(cp);
+  APK_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1);
+  return APK_OK;
+}
+
+int apk_reduce_scatter(const apk_comm* comm, const void* in, void* out, uint64_t out_bytes, int32_t dtype, int32_t reduce_op, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (out_bytes == 0) return APK_OK;
+  if (in == nullptr || out == nullptr) return fail(APK_ERR_ARG, "null buffer");
+  if (dtype != APK_BF16 && dtype != APK_F32) return fail(APK_ERR_ARG, "dtype must be bf16 or f32");
+  if (reduce_op != APK_REDUCE_SUM && reduce_op != APK_REDUCE_AVG) return fail(APK_ERR_ARG, "reduce_op must be sum or avg");
+  if (((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15u) != 0) return fail(APK_ERR_ARG, "buffers must be 16-byte aligned");
+  if (comm == nullptr) return fail(APK_ERR_ARG, "comm is null");
+  apk::CParams cp;
+  int rc = coll_common(comm, out_bytes, out_bytes * (uint64_t)comm->world, &cp, stream);
+  if (rc != APK_OK) return rc;
+  cp.src = reinterpret_cast<const uint8_t*>(in);
+  cp.out = reinterpret_cast<uint8_t*>(out);
+  cp.fp32 = dtype == APK_F32;
+  cp.reduce_scale = reduce_op == APK_REDUCE_AVG ? 1.0f / (float)comm->world : 1.0f;
+  if (comm->world > 1) {
+    const uint64_t max_tiles = (comm->flag_bytes - kFlagRsOffset) / 4 / (uint64_t)comm->world;
+    cp.flag_stride = (int32_t)max_tiles;   // flag (source, tile 0) of the per-tile flag array
+    for (int r = 0; r < comm->world; ++r) cp.flag_peer[r] = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(comm->flags[r]) + kFlagRsOffset);
+    cp.flag_local = cp.flag_peer[comm->rank];
+  }
+  DeviceInfo di;
+  device_info(&di);
+  apk::reduce_scatter_kernel<<<di.sms, apk::COLL_THREADS, 0, stream>>>(cp);
+  APK_CUDA(cudaGetLastError());
+  g_launches.fetch_add(1);
+  return APK_OK;
 }
 
 int apk_check_status(const apk_comm* comm, void* stream_, uint32_t* raw) {

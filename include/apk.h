@@ -165,6 +165,19 @@ int apk_ag_gemm(const apk_comm* comm, const apk_ag_gemm_args* args, void* stream
 int apk_gemm_rs(const apk_comm* comm, const apk_gemm_rs_args* args, void* stream);
 
 /*
+ * Stand-alone collectives over the same arena, signal pad and epoch (each call is one collective:
+ * increment comm->epoch). out = every rank's shard, ordered by rank; every shard has shard_bytes
+ * (a multiple of 16). Replaces _low_contention_all_gather (autoparallel/asynctp_ops.py:1524-1610).
+ */
+int apk_all_gather(const apk_comm* comm, const void* shard, void* out, uint64_t shard_bytes, void* stream);
+/*
+ * `in` holds world parts of out_bytes each; out = sum (or mean) over ranks of part [rank]. Elements are
+ * bf16 or fp32, accumulated in fp32. Replaces _low_contention_reduce_scatter (:1613-1702).
+ */
+int apk_reduce_scatter(const apk_comm* comm, const void* in, void* out, uint64_t out_bytes, int32_t dtype,
+                       int32_t reduce_op, void* stream);
+
+/*
  * apk_ag_gemm without caller-provided scratch. It has no counterpart in the reference.
  *
  * For callers that cannot allocate device memory around the op: a serving runtime that has

@@ -133,6 +133,18 @@ def _worker(rank, world, golden):
     )[rank]
     assert out.shape == ref.shape and orc.rel_fro_error(out, ref.double()) <= FP8_TOL
 
+    # ---- stand-alone collectives over the same arena and flags
+    x = orc.activations(110 + rank, 300, 264).to(dev)
+    got = ns._low_contention_all_gather(x, g)
+    want = torch.cat([orc.activations(110 + r, 300, 264) for r in range(world)])
+    assert torch.equal(got.cpu(), want)
+    for dt, tol in ((torch.bfloat16, 1e-2), (torch.float32, 1e-6)):
+        ys = [orc.activations(120 + r, 64 * world, 200, dt) for r in range(world)]
+        for op in ("sum", "avg"):
+            got = ns._low_contention_reduce_scatter(ys[rank].to(dev), op, g)
+            want = sum(y.double() for y in ys).chunk(world)[rank] / (world if op == "avg" else 1)
+            assert got.shape == want.shape and got.dtype == dt and orc.rel_fro_error(got, want) <= tol
+
     # ---- many back-to-back calls: the two halves of the arena and the epoch flags hold up
     A = orc.activations(rank, 1024, 1024).to(dev)
     W = orc.weights(7, 1024, 512).to(dev)

@@ -140,6 +140,74 @@ def test_all_gather_last_dim_receive_side_on_one_gpu(group):
         assert torch.equal(stacked[:rows], h.shards[0]) and torch.equal(stacked[rows:], h.shards[1])
 
 
+def test_stand_alone_collectives_single_rank(group):
+    x = torch.randn(37, 24, device="cuda").bfloat16()
+    assert torch.equal(torch.ops._ap_symm_mem._low_contention_all_gather(x, group), x)
+    y = torch.randn(16, 8, device="cuda")
+    torch.testing.assert_close(torch.ops._ap_symm_mem._low_contention_reduce_scatter(y, "avg", group), y)
+    with pytest.raises(ValueError, match="reduce_op must be sum or avg"):
+        torch.ops._ap_symm_mem._low_contention_reduce_scatter(y, "max", group)
+
+
+def test_stand_alone_collectives_receive_side_on_one_gpu(group):
+    """Rank 0 of a 4-rank all-gather and reduce-scatter on one GPU: the peers' staged shards / partial
+    parts and their flags are placed beforehand, so the pull, the pushes and the fp32 sum all run."""
+    from autoparallel_b200 import _native as nat
+
+    L = nat.lib()
+    world, nbytes = 4, 300 * 264 * 2
+    shards = [torch.randn(300, 264, device="cuda").bfloat16() for _ in range(world)]
+    half = ((world * nbytes + 4095) // 4096) * 4096
+    arenas = [torch.zeros(2 * half, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    pads = [torch.zeros(1 << 17, dtype=torch.int32, device="cuda") for _ in range(world)]
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ctrl = torch.zeros(1024, dtype=torch.int32, device="cuda")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def comm(epoch):
+        c = nat.ApkComm()
+        c.rank, c.world = 0, world
+        for r in range(world):
+            c.data[r], c.flags[r] = arenas[r].data_ptr(), pads[r].data_ptr()
+        c.data_bytes, c.flag_bytes = 2 * half, pads[0].numel() * 4
+        c.ctrl, c.ctrl_bytes = ctrl.data_ptr(), ctrl.numel() * 4
+        c.status, c.epoch, c.timeout_s = status.data_ptr(), epoch, 5.0
+        return c
+
+    raw = C.c_uint32(0)
+    # all-gather: peers r staged their shard at the start of their arena half; "staged" flags live 32 words apart
+    for r in range(1, world):
+        for h in range(2):
+            arenas[r][h * half: h * half + nbytes] = shards[r].view(torch.uint8).view(-1)
+        pads[0][r * 32] = 1000
+    for epoch in (1, 2):
+        out = torch.zeros(world * 300, 264, dtype=torch.bfloat16, device="cuda")
+        c = comm(epoch)
+        assert L.apk_all_gather(C.byref(c), C.c_void_p(shards[0].data_ptr()), C.c_void_p(out.data_ptr()), nbytes, stream) == 0, L.apk_last_error()
+        assert L.apk_check_status(C.byref(c), stream, C.byref(raw)) == nat.APK_OK, L.apk_last_error()
+        assert torch.equal(out, torch.cat(shards))
+        assert int(pads[2][0]) == epoch        # rank 0 told rank 2 that its shard is staged
+    # reduce-scatter: peers' parts for rank 0 wait in slots 1..3 of rank 0's arena half, flags (source, tile 0) raised
+    full = [torch.randn(world * 300, 264, device="cuda").bfloat16() for _ in range(world)]
+    max_tiles = (pads[0].numel() * 4 - 4096) // 4 // world
+    for r in range(1, world):
+        for h in range(2):
+            arenas[0][h * half + r * nbytes: h * half + (r + 1) * nbytes] = full[r][:300].contiguous().view(torch.uint8).view(-1)
+        pads[0][1024 + r * max_tiles] = 1000
+    want = sum(f[:300].double() for f in full) / world
+    for epoch in (3, 4):
+        out = torch.zeros(300, 264, dtype=torch.bfloat16, device="cuda")
+        c = comm(epoch)
+        assert L.apk_reduce_scatter(C.byref(c), C.c_void_p(full[0].data_ptr()), C.c_void_p(out.data_ptr()), nbytes,
+                                    nat.APK_BF16, nat.APK_REDUCE_AVG, stream) == 0, L.apk_last_error()
+        assert L.apk_check_status(C.byref(c), stream, C.byref(raw)) == nat.APK_OK, L.apk_last_error()
+        assert _orc().rel_fro_error(out, want.cpu()) <= BF16_TOL
+        off = (epoch & 1) * half
+        sent = arenas[2][off: off + nbytes].view(torch.bfloat16).view(300, 264)      # slot 0 of rank 2's arena
+        assert torch.equal(sent, full[0][600:900])
+        assert int(pads[2][1024]) == epoch
+
+
 def test_golden_all_gather_matmul(group, golden):
     """bf16 golden cases: the gathered A the reference produced, times the Bs, must give its outputs."""
     orc = _orc()
