@@ -920,7 +920,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
 
       if (p.mode == MODE_RS && own) ++own_seen;
       if (rs_remote) {
-        // The owner's flag for this tile is released once three newer tiles are queued behind it,
+        // The owner's flag for this tile is released (two tiles at a time) once the queue of four is full,
         // before this CTA waits on its peers, or after the loop.
         push_pending(p.rs_flag_peer[ti.chunk] + (size_t)p.rank * p.rs_max_tiles + ti.tile_in_chunk, !use_tma);
       }

@@ -74,7 +74,8 @@ typedef struct {
   void* data[APK_MAX_WORLD];
   void* flags[APK_MAX_WORLD];
   uint64_t data_bytes;  /* size of each data arena (both halves together) */
-  uint64_t flag_bytes;  /* size of each signal pad, at least 4096 */
+  uint64_t flag_bytes;  /* size of each signal pad: 4096 bytes of per-rank flags, then world x T per-tile flags
+                           (u32); at least 8192, T limits the tiles of one reduce-scatter chunk */
   void* ctrl;           /* local device scratch for per-call counters */
   uint64_t ctrl_bytes;
   uint32_t* status;     /* local device word; 0 while no device wait has timed out */

@@ -9,10 +9,10 @@ Pinning: the reference's own tests hold no vector for this path. The oracle is p
 outputs of the reference's fallbacks themselves, run on CPU/gloo with two ranks by
 ``tests/golden/make_golden.py`` (fixtures in ``tests/golden/``): all-gather-matmul (every
 gather_dim, return_A), matmul-reduce-scatter (sum / avg, every scatter_dim), and the scaled
-variants with tensor-wise scales. Row-wise fp8 scaling cannot be run through the reference on
-CPU (``torch._scaled_mm`` rejects row-wise scales there), so for row-wise scales parity is
-unpinned by the reference and rests on the restatement in ``scaled_mm`` below (checked on GPU
-against ``torch._scaled_mm`` itself by the gpu tests).
+matmul-reduce-scatter with tensor-wise scales. Parity is UNPINNED by the reference for two parts
+that it cannot run on CPU: the scaled all-gather fallback (gloo has no fp8 all-gather) and row-wise
+fp8 scaling (CPU ``torch._scaled_mm`` accepts per-tensor scales only); those rest on the
+restatement in ``scaled_mm`` below, which the gpu tests check against ``torch._scaled_mm`` itself.
 
 Two forms of every op:
 * ``*_local``: one process holds every rank's operands in lists (collectives become cat / sum);
