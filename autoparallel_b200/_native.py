@@ -51,6 +51,7 @@ EXPORTED_SYMBOLS = (
     "apk_ag_gemm_static",
     "apk_all_gather",
     "apk_reduce_scatter",
+    "apk_debug_schedule",
     "apk_check_status",
     "apk_launch_count",
     "apk_pair_launch_count",
@@ -168,6 +169,8 @@ def lib() -> C.CDLL:
     L.apk_all_gather.restype = C.c_int
     L.apk_reduce_scatter.argtypes = [C.POINTER(ApkComm), C.c_void_p, C.c_void_p, C.c_uint64, C.c_int32, C.c_int32, C.c_void_p]
     L.apk_reduce_scatter.restype = C.c_int
+    L.apk_debug_schedule.argtypes = [C.c_int32] * 5 + [C.POINTER(C.c_int32)] + [C.c_int32] * 3 + [C.POINTER(C.c_int32), C.c_int32]
+    L.apk_debug_schedule.restype = C.c_int
     L.apk_check_status.argtypes = [C.POINTER(ApkComm), C.c_void_p, C.POINTER(C.c_uint32)]
     L.apk_launch_count.restype = C.c_uint64
     L.apk_pair_launch_count.restype = C.c_uint64

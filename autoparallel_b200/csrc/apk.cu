@@ -264,6 +264,21 @@ constexpr uint64_t kFlagRsOffset = 4096;  // bytes: staged flags live below, per
 
 }  // namespace
 
+// The order in which one CTA (or CTA pair) enumeration visits the tiles, computed on the host with the
+// very functions the kernel uses. For tests of the schedule; needs no GPU.
+template <int BN, bool PAIR>
+int schedule_rows(const apk::KParams& kp, int crank, int32_t* out, int capacity) {
+  const apk::Sched sc = apk::make_sched<BN, PAIR>(kp);
+  if (out != nullptr) {
+    for (int t = 0; t < sc.total_tiles && t < capacity; ++t) {
+      const apk::TileInfo ti = apk::decode_tile<BN, PAIR>(kp, sc, t, crank);
+      int32_t* r = out + 6 * (size_t)t;
+      r[0] = ti.chunk; r[1] = ti.mt; r[2] = ti.b; r[3] = ti.n0; r[4] = ti.tile_in_chunk; r[5] = ti.rows_valid;
+    }
+  }
+  return sc.total_tiles;
+}
+
 extern "C" {
 
 int apk_abi_version(void) { return APK_ABI_VERSION; }
@@ -612,6 +627,27 @@ int apk_reduce_scatter(const apk_comm* comm, const void* in, void* out, uint64_t
   APK_CUDA(cudaGetLastError());
   g_launches.fetch_add(1);
   return APK_OK;
+}
+
+int apk_debug_schedule(int32_t mode, int32_t world, int32_t rank, int32_t rows_per_rank, int32_t nB, const int32_t* N,
+                       int32_t last_dim, int32_t pair, int32_t crank, int32_t* out, int32_t capacity) {
+  if (nB < 1 || nB > APK_MAX_B || N == nullptr || world < 1 || world > APK_MAX_WORLD) return fail(APK_ERR_ARG, "bad arguments");
+  apk::KParams kp;
+  memset(&kp, 0, sizeof(kp));
+  kp.mode = mode;
+  kp.ws = world;
+  kp.rank = rank;
+  kp.nB = nB;
+  kp.rows_per_rank = rows_per_rank;
+  kp.ag_ksplit = (mode == apk::MODE_AG && last_dim) ? 1 : 0;
+  kp.rs_colsplit = (mode == apk::MODE_RS && last_dim) ? 1 : 0;
+  int max_n = 0;
+  for (int b = 0; b < nB; ++b) {
+    kp.N[b] = N[b];
+    max_n = N[b] > max_n ? N[b] : max_n;
+  }
+  if (max_n <= 128) return pair ? fail(APK_ERR_ARG, "pairs need 256-column tiles") : schedule_rows<128, false>(kp, 0, out, capacity);
+  return pair ? schedule_rows<256, true>(kp, crank, out, capacity) : schedule_rows<256, false>(kp, 0, out, capacity);
 }
 
 int apk_check_status(const apk_comm* comm, void* stream_, uint32_t* raw) {

@@ -145,7 +145,7 @@ struct Sched {
 };
 
 template <int BN, bool PAIR = false>
-__device__ __forceinline__ Sched make_sched(const KParams& p) {
+__host__ __device__ __forceinline__ Sched make_sched(const KParams& p) {
   Sched s;
   s.nt_total = 0;
 #pragma unroll
@@ -169,7 +169,7 @@ __device__ __forceinline__ Sched make_sched(const KParams& p) {
 // which a strict "one peer per step" order does not.
 // With PAIR a unit is two vertically adjacent tiles (same columns); `crank` (0 or 1) picks this CTA's.
 template <int BN, bool PAIR = false>
-__device__ __forceinline__ TileInfo decode_tile(const KParams& p, const Sched& s, int t, int crank = 0) {
+__host__ __device__ __forceinline__ TileInfo decode_tile(const KParams& p, const Sched& s, int t, int crank = 0) {
   TileInfo ti;
   int nt;
   if (p.mode == MODE_PLAIN || p.ws == 1 || p.ag_ksplit) {
@@ -234,8 +234,9 @@ __device__ __forceinline__ TileInfo decode_tile(const KParams& p, const Sched& s
     }
   }
   ti.n0 = nt * BN;
-  ti.rows_valid = min(BM, p.rows_per_rank - ti.mt * BM);
-  ti.n_valid = min(BN, p.N[ti.b] - ti.n0);
+  const int rows_left = p.rows_per_rank - ti.mt * BM, cols_left = p.N[ti.b] - ti.n0;
+  ti.rows_valid = rows_left < BM ? rows_left : BM;
+  ti.n_valid = cols_left < BN ? cols_left : BN;
   return ti;
 }
 

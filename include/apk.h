@@ -202,6 +202,16 @@ int apk_ag_gemm_static(const apk_comm* comm, const apk_ag_gemm_args* args, void*
 /* Synchronises `stream`, reads the status word, clears it; APK_ERR_TIMEOUT if it was set. */
 int apk_check_status(const apk_comm* comm, void* stream, uint32_t* raw);
 
+/*
+ * Test utility, no GPU needed: the order in which the persistent kernel's CTAs (pair = 0) or CTA pairs
+ * (pair = 1, crank = rank inside the pair) enumerate the tiles of a problem, computed with the kernel's
+ * own scheduling functions. mode: 0 plain, 1 all-gather, 2 reduce-scatter; last_dim: the K-split /
+ * column-split variants. Writes up to `capacity` rows of 6 ints (chunk, row block, operand, first
+ * column, tile index inside the chunk, valid rows) and returns the number of scheduling units.
+ */
+int apk_debug_schedule(int32_t mode, int32_t world, int32_t rank, int32_t rows_per_rank, int32_t nB, const int32_t* N,
+                       int32_t last_dim, int32_t pair, int32_t crank, int32_t* out, int32_t capacity);
+
 /* Kernels launched by this library in this process so far (memsets not counted). */
 uint64_t apk_launch_count(void);
 /* ... of which launched as clusters of two CTAs (tcgen05 cta_group::2). */

@@ -507,6 +507,58 @@ def test_reduce_scatter_receive_side_on_one_gpu(group, world, M, K, N):
             assert int(pads[d][1024 + 0]) == epoch   # flag (source 0, tile 0) released with the epoch
 
 
+def test_reduce_scatter_fp32_partials_receive_side_on_one_gpu(group):
+    """fp32 outputs travel as fp32 partials in row-major slots (the bf16 path uses the blocked arena):
+    rank 1 of a three-rank group on one GPU, peers' partials and flags placed beforehand."""
+    from autoparallel_b200 import _native as nat
+
+    L = nat.lib()
+    orc = _orc()
+    world, rank, M, K, N = 3, 1, 3 * 200, 128, 72
+    rows, slot_rows = M // world, 256
+    A, B = orc.activations(0, M, K), orc.weights(7, K, N)
+    peers = {r: torch.randn(rows, N) for r in (0, 2)}
+    args0 = nat.ApkGemmRsArgs()
+    args0.M, args0.B.N, args0.B.out_dtype = M, N, nat.APK_F32
+    half = int(L.apk_gemm_rs_arena_bytes(C.byref(args0), world))
+    assert half == world * slot_rows * N * 4
+    arenas = [torch.zeros(2 * half, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    for h in range(2):
+        for src, part in peers.items():
+            off = h * half + src * slot_rows * N * 4
+            arenas[rank][off: off + rows * N * 4] = part.cuda().view(torch.uint8).view(-1)
+    pads = [torch.zeros(1 << 17, dtype=torch.int32, device="cuda") for _ in range(world)]
+    pads[rank][1024:] = 1000
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ctrl = torch.zeros(1024, dtype=torch.int32, device="cuda")
+    Ad, Bd = A.cuda(), B.cuda()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    full64 = A.double() @ B.double()
+    for epoch in (1, 2):
+        out = torch.full((rows, N), float("nan"), dtype=torch.float32, device="cuda")
+        comm = nat.ApkComm()
+        comm.rank, comm.world = rank, world
+        for r in range(world):
+            comm.data[r], comm.flags[r] = arenas[r].data_ptr(), pads[r].data_ptr()
+        comm.data_bytes, comm.flag_bytes = 2 * half, pads[0].numel() * 4
+        comm.ctrl, comm.ctrl_bytes = ctrl.data_ptr(), ctrl.numel() * 4
+        comm.status, comm.epoch, comm.timeout_s = status.data_ptr(), epoch, 5.0
+        args = nat.ApkGemmRsArgs()
+        args.dtype, args.M, args.K, args.reduce_op = nat.APK_BF16, M, K, nat.APK_REDUCE_SUM
+        args.A, args.lda = Ad.data_ptr(), K
+        args.B.B, args.B.ldb, args.B.n_major, args.B.N = Bd.data_ptr(), N, 1, N
+        args.B.out, args.B.ldo, args.B.out_dtype = out.data_ptr(), N, nat.APK_F32
+        assert L.apk_gemm_rs(C.byref(comm), C.byref(args), stream) == nat.APK_OK, L.apk_last_error()
+        raw = C.c_uint32(0)
+        assert L.apk_check_status(C.byref(comm), stream, C.byref(raw)) == nat.APK_OK, L.apk_last_error()
+        ref64 = full64[rank * rows:(rank + 1) * rows] + sum(p.double() for p in peers.values())
+        assert orc.rel_fro_error(out, ref64) <= 1e-5
+        # the part sent to rank 2: slot `rank` of its arena, fp32 row-major
+        off = (epoch & 1) * half + rank * slot_rows * N * 4
+        sent = arenas[2][off: off + rows * N * 4].view(torch.float32).view(rows, N)
+        assert orc.rel_fro_error(sent, full64[2 * rows:]) <= 1e-5
+
+
 def test_device_wait_times_out_cleanly(group):
     """A two-rank reduce-scatter whose 'peer' is this GPU's own memory and never answers: the
     wait for the peer's partial runs out after timeout_s, the kernel frees its resources and
