@@ -11,7 +11,12 @@ from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent / "csrc"
 SOURCES = [CSRC / "apk.cu"]
-HEADERS = [CSRC / "gemm_kernel.cuh", CSRC / "ptx.cuh", CSRC.parent.parent / "include" / "apk.h"]
+HEADERS = [
+    CSRC / "gemm_kernel.cuh",
+    CSRC / "collectives_kernel.cuh",
+    CSRC / "ptx.cuh",
+    CSRC.parent.parent / "include" / "apk.h",
+]
 OUT = CSRC / "libapk.so"
 
 NVCC_FLAGS = [
