@@ -6,13 +6,19 @@ only by ``tests/``, by ``__graft_entry__.smoke()`` and by the CPU-baseline legs 
 nothing in ``autoparallel_b200`` imports it and the product never computes through it.
 
 Pinning: the reference's own tests hold no vector for this path. The oracle is pinned against
-outputs of the reference's fallbacks themselves, run on CPU/gloo with two ranks by
-``tests/golden/make_golden.py`` (fixtures in ``tests/golden/``): all-gather-matmul (every
-gather_dim, return_A), matmul-reduce-scatter (sum / avg, every scatter_dim), and the scaled
-matmul-reduce-scatter with tensor-wise scales. Parity is UNPINNED by the reference for two parts
-that it cannot run on CPU: the scaled all-gather fallback (gloo has no fp8 all-gather) and row-wise
-fp8 scaling (CPU ``torch._scaled_mm`` accepts per-tensor scales only); those rest on the
-restatement in ``scaled_mm`` below, which the gpu tests check against ``torch._scaled_mm`` itself.
+outputs of the reference's fallbacks themselves (fixtures in ``tests/golden/``):
+
+* ``tests/golden/make_golden.py``, two gloo ranks on CPU: all-gather-matmul (every gather_dim,
+  return_A), matmul-reduce-scatter (sum / avg, every scatter_dim) and the scaled
+  matmul-reduce-scatter with tensor-wise scales;
+* ``tests/golden/make_golden_fp8.py``, two ranks over torch's in-process threaded process group
+  (gloo cannot move fp8): the scaled all-gather-matmul with tensor-wise scales on stock torch, and,
+  with a CPU stand-in for the row-wise ``aten::_scaled_mm`` that CPU torch lacks, the reference's
+  handling of row-wise sharded / replicated scales and the row-wise scaled reduce-scatter.
+
+Parity is UNPINNED by a reference run for one part only: the row-wise arithmetic of
+``_scaled_mm`` itself, restated in ``scaled_mm`` below, which the gpu tests check against
+``torch._scaled_mm`` on the device.
 
 Two forms of every op:
 * ``*_local``: one process holds every rank's operands in lists (collectives become cat / sum);

@@ -17,3 +17,10 @@ def golden():
     import torch
 
     return torch.load(ROOT / "tests" / "golden" / "asynctp_golden.pt", weights_only=False)
+
+
+@pytest.fixture(scope="session")
+def golden_fp8():
+    import torch
+
+    return torch.load(ROOT / "tests" / "golden" / "asynctp_golden_fp8.pt", weights_only=False)

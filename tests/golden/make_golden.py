@@ -9,7 +9,8 @@ its Meta/fallback kernels directly (the dispatcher has no CPU key for them):
 ``_fused_all_gather_matmul_fallback``, ``_fused_matmul_reduce_scatter_fallback`` and, with
 tensor-wise scales (the only scaling CPU ``torch._scaled_mm`` accepts),
 ``_fused_scaled_matmul_reduce_scatter_fallback``. ``_fused_all_gather_scaled_matmul_fallback``
-cannot run on CPU: gloo has no fp8 all-gather.
+cannot run over gloo, which has no fp8 all-gather: ``make_golden_fp8.py`` beside this file covers it
+over an in-process threaded process group.
 Inputs and every rank's outputs are stored, so the oracle tests need neither the reference nor
 a matching RNG.
 """

@@ -113,3 +113,51 @@ def test_scaled_all_gather_scale_modes():
     assert orc.rel_fro_error(o3, ref) < 1e-6
     with pytest.raises(ValueError):
         orc.all_gather_scaled_matmul_local(shards, [B], [torch.rand(3, 1)] * 2, [sb], 0, [None], [None], [torch.float32])
+
+
+# ---- fp8 fixtures made by tests/golden/make_golden_fp8.py (reference fallbacks :873-944 and :1242-1290 over a
+# ---- threaded two-rank process group; see that script for what "torch-cpu" and "stand-in" mean)
+_DT = {"torch.bfloat16": torch.bfloat16, "torch.float32": torch.float32}
+
+
+def _close_fp8(o, g):
+    assert o.shape == g.shape and o.dtype == g.dtype
+    if o.dtype == torch.float32:
+        torch.testing.assert_close(o, g, rtol=1e-5, atol=1e-5)
+    else:  # one bf16 ulp: the two sides may round a differently-ordered fp32 sum
+        torch.testing.assert_close(o.float(), g.float(), rtol=2 ** -7, atol=1e-3)
+
+
+def test_fp8_fixture_is_complete(golden_fp8):
+    r0 = golden_fp8["ranks"][0]
+    assert golden_fp8["world"] == 2 and len(golden_fp8["ranks"]) == 2
+    assert sum(c["kind"] == "sag_mm" and c["scaled_mm"] == "torch-cpu" for c in r0) == 3
+    assert sum(c["kind"] == "sag_mm" and c["scaled_mm"] == "stand-in" for c in r0) == 6
+    assert sum(c["kind"] == "smm_rs" for c in r0) == 3
+    assert {c["mode"] for c in r0} == {"tensor", "row_sharded", "row_replicated", "row"}
+
+
+def test_all_gather_scaled_matmul_matches_reference(golden_fp8):
+    for c0, c1 in _cases(golden_fp8, "sag_mm"):
+        Bs = [bt.t() for bt in c0["Bs_t"]]
+        A, outs = orc.all_gather_scaled_matmul_local(
+            [c0["A_shard"], c1["A_shard"]], Bs, [c0["A_scale"], c1["A_scale"]], c0["B_scales"], c0["gather_dim"],
+            c0["biases"], c0["result_scales"], [_DT[d] for d in c0["out_dtypes"]],
+        )
+        for rec in (c0, c1):
+            what = (rec["mode"], rec["shape"], rec["gather_dim"])
+            assert A.shape == rec["A_out"].shape and A.dtype == rec["A_out"].dtype, what
+            assert torch.equal(A.contiguous().view(torch.uint8), rec["A_out"].view(torch.uint8)), what
+            assert len(outs) == len(rec["outs"])
+            for o, g in zip(outs, rec["outs"]):
+                _close_fp8(o, g)
+
+
+def test_rowwise_scaled_matmul_reduce_scatter_matches_reference(golden_fp8):
+    for c0, c1 in _cases(golden_fp8, "smm_rs"):
+        outs = orc.scaled_matmul_reduce_scatter_local(
+            [c0["A"], c1["A"]], [c0["B_t"].t(), c1["B_t"].t()], [c0["A_scale"], c1["A_scale"]],
+            [c0["B_scale"], c1["B_scale"]], c0["op"], c0["scatter_dim"], c0["output_shape"], out_dtype=torch.bfloat16,
+        )
+        for o, rec in zip(outs, (c0, c1)):
+            _close_fp8(o, rec["out"])
