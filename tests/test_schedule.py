@@ -87,3 +87,101 @@ def test_last_dim_variants():
     # column-split reduce-scatter: chunks are column ranges of ALL rows
     s = schedule(RS, 4, 1, 640, [256], last_dim=1)
     assert len(s) == 4 * 5 * 1 and set(s[:, 0]) == {0, 1, 2, 3}
+
+
+# ------------------------------------------------------------------------------------------------
+# Properties over random shapes (the fixed cases above pin the exact order; these guard the
+# invariants the device protocol relies on for every shape the host code can pass down).
+# ------------------------------------------------------------------------------------------------
+from hypothesis import given, settings, strategies as st  # noqa: E402
+
+
+def _widths(draw, pair):
+    n = draw(st.integers(1, 3))
+    if pair:
+        return [256 * draw(st.integers(1, 4)) for _ in range(n)]
+    return [8 * draw(st.integers(1, 130)) for _ in range(n)]
+
+
+@st.composite
+def _shapes(draw, modes=(PLAIN, AG, RS)):
+    mode = draw(st.sampled_from(modes))
+    world = 1 if mode == PLAIN else draw(st.sampled_from([1, 2, 3, 4, 8]))
+    rank = draw(st.integers(0, world - 1))
+    pair = draw(st.booleans())
+    rows = 256 * draw(st.integers(1, 12)) if pair else draw(st.integers(1, 1500))
+    Ns = _widths(draw, pair)
+    if mode == RS:
+        Ns = Ns[:1]
+    last_dim = draw(st.booleans()) if mode != PLAIN else False
+    return mode, world, rank, rows, Ns, int(last_dim), int(pair)
+
+
+def _units(mode, world, rank, rows, Ns, last_dim, pair):
+    """Schedule as a list of scheduling units; a unit is a list of tiles (two for a CTA pair)."""
+    if not pair:
+        return [[tuple(r)] for r in schedule(mode, world, rank, rows, Ns, last_dim)]
+    a = schedule(mode, world, rank, rows, Ns, last_dim, 1, 0)
+    b = schedule(mode, world, rank, rows, Ns, last_dim, 1, 1)
+    return [[tuple(x), tuple(y)] for x, y in zip(a, b)]
+
+
+@settings(max_examples=150, deadline=None)
+@given(_shapes())
+def test_every_tile_is_scheduled_exactly_once(shape):
+    mode, world, rank, rows, Ns, last_dim, pair = shape
+    bn = 128 if max(Ns) <= 128 else 256
+    units = _units(*shape)
+    tiles = [t for u in units for t in u]
+    chunks = range(world) if mode != PLAIN and not (mode == AG and last_dim) else range(1)
+    want = expected_tiles(world, rows, Ns, bn, chunks)
+    assert len(tiles) == len(want) and {t[:4] for t in tiles} == want
+    mt = -(-rows // 128)
+    per_chunk = len(want) // len(chunks)
+    seen = set()
+    for chunk, m, b, n0, tile_in_chunk, rows_valid in tiles:
+        assert 0 <= tile_in_chunk < per_chunk                       # indexes flags and arena blocks of one chunk
+        assert (chunk, tile_in_chunk) not in seen                   # ... without collisions
+        seen.add((chunk, tile_in_chunk))
+        assert rows_valid == (128 if m < mt - 1 or rows % 128 == 0 else rows % 128)
+        assert n0 % bn == 0 and 0 <= n0 < Ns[b]
+
+
+@settings(max_examples=60, deadline=None)
+@given(_shapes(modes=(RS,)))
+def test_reduce_scatter_waits_only_on_earlier_positions(shape):
+    """Progress argument of the reduce-scatter: a unit that owns its tile waits for the peers'
+    partials of the same tile. On every peer that tile sits at an EARLIER position of the peer's
+    list, and sends never wait on anything, so by induction over positions no set of co-resident
+    CTAs can wait on each other in a cycle."""
+    mode, world, rank, rows, Ns, last_dim, pair = shape
+    if world == 1:
+        return
+    per_rank = [_units(mode, world, r, rows, Ns, last_dim, pair) for r in range(world)]
+    pos = [{t[:4]: i for i, u in enumerate(units) for t in u} for units in per_rank]
+    ident = [{t[:4]: t[4] for u in units for t in u} for units in per_rank]
+    for r in range(world):
+        for i, unit in enumerate(per_rank[r]):
+            for t in unit:
+                if t[0] != r:
+                    continue
+                for s in range(world):
+                    if s != r:
+                        assert pos[s][t[:4]] < i, (r, s, t)
+                        assert ident[s][t[:4]] == t[4]           # both sides name the tile's flag alike
+    # all ranks walk lists of the same length with own / remote tiles at the same positions
+    kinds = [[u[0][0] == r for u in per_rank[r]] for r in range(world)]
+    assert all(k == kinds[0] for k in kinds)
+
+
+@settings(max_examples=60, deadline=None)
+@given(_shapes(modes=(AG,)))
+def test_all_gather_starts_on_local_rows(shape):
+    mode, world, rank, rows, Ns, last_dim, pair = shape
+    units = _units(*shape)
+    if last_dim:
+        assert all(t[0] == 0 for u in units for t in u)             # one pass; K slices switch sources inside a tile
+        return
+    own = [i for i, u in enumerate(units) if u[0][0] == rank]
+    assert own == list(range(len(own)))                             # nothing to wait for at the start
+    assert len(own) * world == len(units)
