@@ -13,7 +13,8 @@ Protocol facts the kernels rely on (kept here because this module owns ``epoch``
 * the data arena is used in two halves selected by ``epoch & 1``; in every op each rank waits
   for a signal that every other rank produces during the same op, so a rank that has reached
   op ``e + 2`` knows that all peers have finished op ``e`` and may overwrite that half;
-* flags carry epoch values and are compared with ``>=``, so they are never reset.
+* flags carry epoch values and are compared with ``>=`` (wrap-safe), so they are never reset;
+  when the arena grows, the new signal pad is zero and the epoch restarts from zero with it.
 """
 from __future__ import annotations
 
@@ -126,6 +127,10 @@ class GroupWorkspace:
             self.handles.flags = self._exchange(self._local_flags)
         self.handles.data_bytes = need
         self.handles.flag_bytes = FLAG_PAD_BYTES
+        # A zero-filled pad starts a new epoch sequence (all ranks grow in the same call, so they
+        # agree): flags are compared wrap-safe, which holds only while flag and epoch are less
+        # than 2**31 ops apart, and zeros next to an old epoch count need not be.
+        self.epoch = 0
         dist.barrier(group=self.group)
 
     # ------------------------------------------------------------------ per call

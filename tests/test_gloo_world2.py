@@ -131,6 +131,12 @@ def _workspace_worker(rank, world):
     assert (c1.epoch, c2.epoch) == (1, 2) and c1.world == world and c1.rank == rank
     assert c1.data[1 - rank] == symm.peer_handles(g).data[1 - rank]
     assert c1.ctrl_bytes >= 512 and c1.timeout_s == symm.DEFAULT_TIMEOUT_S
+    # a grown arena comes with a zeroed signal pad: the epoch sequence restarts on every rank
+    w.ensure(40_000, 512)
+    assert symm.peer_handles(g).data_bytes >= 2 * 40_960
+    assert w.next_comm().epoch == 1
+    w.ensure(40_000, 512)
+    assert w.next_comm().epoch == 2
     symm.shutdown()
     assert fake.imports == 0 and not fake.live
 
