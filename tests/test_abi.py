@@ -74,3 +74,70 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setenv("APK_LIB", str(tmp_path / "nope.so"))
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         nat.lib()
+
+
+_C_PROBE = r"""
+#include <stddef.h>
+#include <stdio.h>
+#include "apk.h"
+#define F(T, f) printf(#T "." #f " %zu\n", offsetof(T, f))
+int main(void) {
+  printf("sizeof.apk_comm %zu\nsizeof.apk_operand %zu\nsizeof.apk_ag_gemm_args %zu\nsizeof.apk_gemm_rs_args %zu\n",
+         sizeof(apk_comm), sizeof(apk_operand), sizeof(apk_ag_gemm_args), sizeof(apk_gemm_rs_args));
+  F(apk_comm, rank); F(apk_comm, world); F(apk_comm, data); F(apk_comm, flags); F(apk_comm, data_bytes);
+  F(apk_comm, flag_bytes); F(apk_comm, ctrl); F(apk_comm, ctrl_bytes); F(apk_comm, status); F(apk_comm, epoch);
+  F(apk_comm, reserved); F(apk_comm, timeout_s);
+  F(apk_operand, B); F(apk_operand, ldb); F(apk_operand, n_major); F(apk_operand, N); F(apk_operand, out);
+  F(apk_operand, ldo); F(apk_operand, out_dtype); F(apk_operand, b_scale_mode); F(apk_operand, b_scale);
+  F(apk_operand, bias); F(apk_operand, bias_dtype); F(apk_operand, reserved); F(apk_operand, result_scale);
+  F(apk_ag_gemm_args, dtype); F(apk_ag_gemm_args, rows_per_rank); F(apk_ag_gemm_args, K); F(apk_ag_gemm_args, nB);
+  F(apk_ag_gemm_args, A_shard); F(apk_ag_gemm_args, lda); F(apk_ag_gemm_args, Bs); F(apk_ag_gemm_args, A_gathered);
+  F(apk_ag_gemm_args, return_A); F(apk_ag_gemm_args, a_scale_mode); F(apk_ag_gemm_args, A_scale);
+  F(apk_ag_gemm_args, A_scale_gathered); F(apk_ag_gemm_args, gather_k); F(apk_ag_gemm_args, reserved);
+  F(apk_gemm_rs_args, dtype); F(apk_gemm_rs_args, M); F(apk_gemm_rs_args, K); F(apk_gemm_rs_args, reduce_op);
+  F(apk_gemm_rs_args, A); F(apk_gemm_rs_args, lda); F(apk_gemm_rs_args, B); F(apk_gemm_rs_args, a_scale_mode);
+  F(apk_gemm_rs_args, scatter_cols); F(apk_gemm_rs_args, A_scale);
+  /* and the library is callable from plain C: version, an argument error, the tile schedule */
+  int32_t n[2] = {1792, 1792};
+  printf("call.abi_version %d\n", apk_abi_version());
+  printf("call.null_comm %d\n", apk_ag_gemm(NULL, NULL, NULL));
+  printf("call.schedule_units %d\n", apk_debug_schedule(1, 8, 3, 4096, 2, n, 0, 0, 0, NULL, 0));
+  printf("const.max_b %d\nconst.max_world %d\n", APK_MAX_B, APK_MAX_WORLD);
+  return 0;
+}
+"""
+
+
+def test_header_is_plain_c_and_ctypes_mirror_matches_field_by_field(L, tmp_path):
+    """include/apk.h compiles as C99 with no torch / CUDA / C++ headers, a plain C program links
+    against the library and calls it, and every field of the ctypes mirror sits where the C
+    compiler puts it."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    src = tmp_path / "probe.c"
+    src.write_text(_C_PROBE)
+    exe = tmp_path / "probe"
+    libdir = Path(nat.LIB_PATH).parent
+    subprocess.run(
+        [gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", f"-I{ROOT / 'include'}", str(src), "-o", str(exe),
+         f"-L{libdir}", "-lapk", f"-Wl,-rpath,{libdir}"],
+        check=True, capture_output=True, text=True,
+    )
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    got = {k: int(v) for k, v in (line.split() for line in out.splitlines())}
+    mirror = {"apk_comm": nat.ApkComm, "apk_operand": nat.ApkOperand, "apk_ag_gemm_args": nat.ApkAgGemmArgs,
+              "apk_gemm_rs_args": nat.ApkGemmRsArgs}
+    n_fields = 0
+    for cname, cls in mirror.items():
+        assert got[f"sizeof.{cname}"] == C.sizeof(cls), cname
+        for fname, _ in cls._fields_:
+            assert got[f"{cname}.{fname}"] == getattr(cls, fname).offset, (cname, fname)
+            n_fields += 1
+    assert n_fields == sum(1 for k in got if k.split(".")[0] in mirror)      # no field of the header left unchecked
+    assert got["call.abi_version"] == 1 and got["call.null_comm"] == nat.APK_ERR_ARG
+    assert got["call.schedule_units"] == 8 * 32 * 14
+    assert (got["const.max_b"], got["const.max_world"]) == (nat.APK_MAX_B, nat.APK_MAX_WORLD)
