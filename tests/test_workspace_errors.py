@@ -1,0 +1,123 @@
+"""Error behaviour of the symmetric workspace (autoparallel_b200/symm.py), on CPU with fakes:
+what the reference gets from torch's workspace (growth refused during CUDA-graph capture,
+torch/distributed/_symmetric_memory/__init__.py:96-134) and what replaces its barrier
+timeouts (a device status word turned into an exception)."""
+import ctypes as C
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from autoparallel_b200 import _native as nat
+from autoparallel_b200 import symm
+
+
+class _Native:
+    """Allocator over host memory plus a scriptable apk_check_status."""
+
+    def __init__(self):
+        self.live, self.status_raw = {}, 0
+
+    def apk_symm_alloc(self, nbytes, out_ptr):
+        buf = (C.c_uint8 * int(nbytes))()
+        self.live[C.addressof(buf)] = buf
+        out_ptr._obj.value = C.addressof(buf)
+        return 0
+
+    def apk_symm_free(self, ptr):
+        self.live.pop(ptr.value, None)
+        return 0
+
+    def apk_symm_export(self, ptr, handle):
+        handle.raw = int(ptr.value).to_bytes(8, "little") + b"\0" * 56
+        return 0
+
+    def apk_symm_import(self, handle, out_ptr):
+        out_ptr._obj.value = int.from_bytes(handle.raw[:8], "little")
+        return 0
+
+    def apk_symm_unimport(self, ptr):
+        return 0
+
+    def apk_check_status(self, comm, stream, raw):
+        raw._obj.value = self.status_raw
+        return nat.APK_ERR_TIMEOUT if self.status_raw else nat.APK_OK
+
+    def apk_last_error(self):
+        return b"device wait timed out: peer partial (detail 3)"
+
+
+@pytest.fixture()
+def group(monkeypatch):
+    from torch.testing._internal.distributed.fake_pg import FakeStore
+
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    dist.init_process_group("fake", store=FakeStore(), rank=1, world_size=4)
+    fake = _Native()
+    monkeypatch.setattr(nat, "lib", lambda: fake)
+    monkeypatch.setattr(symm, "_workspaces", {})
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda *a, **k: None)
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda *a, **k: type("S", (), {"cuda_stream": 0})())
+    yield fake, dist.group.WORLD.group_name
+    dist.destroy_process_group()
+
+
+def test_growth_is_refused_during_graph_capture(group, monkeypatch):
+    fake, g = group
+    w = symm.get_workspace(g, torch.device("cpu"))
+    monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: True)
+    with pytest.raises(RuntimeError, match="cannot grow during CUDA graph capture"):
+        w.ensure(1 << 20, 256)
+    assert not fake.live          # nothing was allocated or exchanged
+
+
+def test_single_rank_group_needs_no_arena(monkeypatch):
+    from torch.testing._internal.distributed.fake_pg import FakeStore
+
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    dist.init_process_group("fake", store=FakeStore(), rank=0, world_size=1)
+    try:
+        fake = _Native()
+        monkeypatch.setattr(nat, "lib", lambda: fake)
+        monkeypatch.setattr(symm, "_workspaces", {})
+        w = symm.get_workspace(dist.group.WORLD.group_name, torch.device("cpu"))
+        w.ensure(1 << 30, 1 << 16)            # only the local counters grow
+        assert not fake.live and w.ctrl.numel() * 4 >= 1 << 16
+        c = w.next_comm()
+        assert (c.world, c.epoch, c.data_bytes) == (1, 1, 0) and not c.data[0]
+    finally:
+        dist.destroy_process_group()
+
+
+def test_groups_larger_than_the_kernel_supports_are_rejected(monkeypatch):
+    from torch.testing._internal.distributed.fake_pg import FakeStore
+
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    dist.init_process_group("fake", store=FakeStore(), rank=0, world_size=16)
+    try:
+        monkeypatch.setattr(symm, "_workspaces", {})
+        with pytest.raises(ValueError, match="at most 8"):
+            symm.get_workspace(dist.group.WORLD.group_name, torch.device("cpu"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_unknown_group_has_no_peer_handles(group):
+    with pytest.raises(KeyError, match="no symmetric workspace"):
+        symm.peer_handles("no-such-group")
+
+
+def test_device_timeout_surfaces_as_an_exception_and_keeps_the_epoch(group):
+    fake, g = group
+    w = symm.get_workspace(g, torch.device("cpu"))
+    w.next_comm()
+    before = w.epoch
+    symm.sync_check()                     # status word clear: nothing happens
+    fake.status_raw = 4 | (3 << 8)        # "peer partial never arrived", detail = source rank 3
+    with pytest.raises(nat.ApkError, match="timed out") as e:
+        symm.sync_check(g)
+    assert e.value.code == nat.APK_ERR_TIMEOUT
+    assert w.epoch == before              # reading the status is not a collective
