@@ -55,6 +55,8 @@ EXPORTED_SYMBOLS = (
     "apk_check_status",
     "apk_launch_count",
     "apk_pair_launch_count",
+    "apk_pair_refusal_count",
+    "apk_set_trace",
 )
 
 
@@ -174,6 +176,9 @@ def lib() -> C.CDLL:
     L.apk_check_status.argtypes = [C.POINTER(ApkComm), C.c_void_p, C.POINTER(C.c_uint32)]
     L.apk_launch_count.restype = C.c_uint64
     L.apk_pair_launch_count.restype = C.c_uint64
+    L.apk_pair_refusal_count.restype = C.c_uint64
+    L.apk_set_trace.argtypes = [C.c_void_p, C.c_uint64]
+    L.apk_set_trace.restype = C.c_int
     for name in ("apk_symm_alloc", "apk_symm_free", "apk_symm_export", "apk_symm_import", "apk_symm_unimport",
                  "apk_ag_gemm", "apk_gemm_rs", "apk_check_status"):
         getattr(L, name).restype = C.c_int

@@ -353,8 +353,8 @@ def _ag_gemm_native(
         raise ValueError("Invalid gather_dim")
     if gather_dim == A_shard.dim() - 1:
         return _ag_gemm_last_dim_native(A_shard, Bs, A_scale, out_dtypes, group_name, return_A)
-    if not 1 <= len(Bs) <= nat.APK_MAX_B:
-        raise NotImplementedError(f"between 1 and {nat.APK_MAX_B} B operands are supported, got {len(Bs)}")
+    if len(Bs) < 1:
+        raise ValueError("at least one B operand is needed")
     group = c10d._resolve_process_group(group_name)
     world = group.size()
     dtype_code = _in_dtype_code(A_shard, "A_shard")
@@ -375,21 +375,32 @@ def _ag_gemm_native(
 
     outs = [A2.new_empty((M, B.shape[1]), dtype=od or B.dtype) for B, od in zip(Bs, out_dtypes)]
     need_gathered = world > 1 or return_A
-    A_full = A2.new_empty((M, K)) if need_gathered else None
+    A_full = A2.new_empty((M, K)) if need_gathered or rows == 0 else None
 
+    if rows == 0:
+        # nothing to gather or multiply: no collective takes place, so the group's epoch must not move
+        return (unflatten(A_full) if return_A else None), [unflatten(o) for o in outs]
+
+    # One launch multiplies the gathered A with up to APK_MAX_B operands. Further operands (the
+    # reference takes any number, autoparallel/asynctp_ops.py:445-454) reuse the gathered A of the
+    # first launch as plain local GEMMs, so nothing crosses NVLink twice.
+    first = min(len(Bs), nat.APK_MAX_B)
+    more = len(Bs) > first
+    if more and A_full is None:
+        A_full = A2.new_empty((M, K))
     wsp = symm.get_workspace(group_name, A2.device)
     args = nat.ApkAgGemmArgs()
     keep: list = [A2]
     args.dtype = dtype_code
     args.rows_per_rank = rows
     args.K = K
-    args.nB = len(Bs)
+    args.nB = first
     args.A_shard = A2.data_ptr()
     args.lda = K
     args.A_gathered = A_full.data_ptr() if A_full is not None else None
-    args.return_A = 1 if return_A else 0
-    for i, (B, out) in enumerate(zip(Bs, outs)):
-        _fill_operand(args.Bs[i], keep, B, out, B_scales[i], biases[i], result_scales[i])
+    args.return_A = 1 if (return_A or more) else 0
+    for i in range(first):
+        _fill_operand(args.Bs[i], keep, Bs[i], outs[i], B_scales[i], biases[i], result_scales[i])
 
     mode = _check_and_verify_fp8_all_gather_scale_mode(A_shard, A_scale, gather_dim, world)
     if mode == _ScaleMode.TENSOR_WISE:
@@ -414,8 +425,47 @@ def _ag_gemm_native(
     wsp.ensure(L.apk_ag_gemm_arena_bytes(C.byref(args), world), L.apk_ctrl_bytes(rows, world))
     comm = wsp.next_comm()
     nat.check(L.apk_ag_gemm(C.byref(comm), C.byref(args), _stream_ptr(A2.device)))
+    if more:
+        full_scale = None
+        if mode == _ScaleMode.ROW_WISE_SHARDED:
+            # the kernel gathered the peers' row scales; add this rank's own rows
+            full_scale = gathered_scale
+            full_scale[wsp.rank * rows:(wsp.rank + 1) * rows].copy_(s)
+        elif mode in (_ScaleMode.TENSOR_WISE, _ScaleMode.ROW_WISE_REPLICATED):
+            full_scale = s
+        for lo in range(first, len(Bs), nat.APK_MAX_B):
+            hi = min(lo + nat.APK_MAX_B, len(Bs))
+            _local_gemm(wsp, A_full, Bs[lo:hi], outs[lo:hi], full_scale, B_scales[lo:hi], biases[lo:hi], result_scales[lo:hi])
     A_ret = unflatten(A_full) if return_A else None
     return A_ret, [unflatten(o) for o in outs]
+
+
+def _local_gemm(
+    wsp: "symm.GroupWorkspace",
+    A: torch.Tensor,
+    Bs: list[torch.Tensor],
+    outs: list[torch.Tensor],
+    A_scale_full: torch.Tensor | None,
+    B_scales: list[torch.Tensor | None],
+    biases: list[torch.Tensor | None],
+    result_scales: list[torch.Tensor | None],
+) -> None:
+    """``outs[i] = A @ Bs[i]`` on this rank alone (at most APK_MAX_B operands): the same kernel
+    on a group of one. ``A_scale_full`` is one scale or one per row of A."""
+    args = nat.ApkAgGemmArgs()
+    keep: list = [A]
+    args.dtype = _in_dtype_code(A, "A")
+    args.rows_per_rank, args.K = A.shape
+    args.nB = len(Bs)
+    args.A_shard = A.data_ptr()
+    args.lda = A.stride(0)
+    for i, (B, out) in enumerate(zip(Bs, outs)):
+        _fill_operand(args.Bs[i], keep, B, out, B_scales[i], biases[i], result_scales[i])
+    if A_scale_full is not None:
+        args.a_scale_mode = nat.APK_SCALE_SCALAR if A_scale_full.numel() == 1 else nat.APK_SCALE_ROWS_REPLICATED
+        args.A_scale = A_scale_full.data_ptr()
+    comm = wsp.local_comm()
+    nat.check(nat.lib().apk_ag_gemm(C.byref(comm), C.byref(args), _stream_ptr(A.device)))
 
 
 def _ag_gemm_last_dim_native(
@@ -432,8 +482,8 @@ def _ag_gemm_last_dim_native(
     autoparallel/asynctp_ops.py:602-669)."""
     if A_scale is not None:
         raise NotImplementedError("scaled all-gather matmul along the last dim is not supported (the reference has none either)")
-    if not 1 <= len(Bs) <= nat.APK_MAX_B:
-        raise NotImplementedError(f"between 1 and {nat.APK_MAX_B} B operands are supported, got {len(Bs)}")
+    if len(Bs) < 1:
+        raise ValueError("at least one B operand is needed")
     group = c10d._resolve_process_group(group_name)
     world = group.size()
     if A_shard.dtype != torch.bfloat16:
@@ -447,8 +497,13 @@ def _ag_gemm_last_dim_native(
         if B.shape[0] != Kc * world:
             raise ValueError(f"B has {B.shape[0]} rows but the gathered A has {Kc * world} columns")
     outs = [A2.new_empty((rows, B.shape[1]), dtype=od or B.dtype) for B, od in zip(Bs, out_dtypes)]
-    need_gathered = world > 1 or return_A
+    first = min(len(Bs), nat.APK_MAX_B)
+    more = len(Bs) > first
+    need_gathered = world > 1 or return_A or more
     stacked = A2.new_empty((world * rows, Kc)) if need_gathered else None   # [world][rows][Kc]
+    if rows == 0:
+        A_ret = A2.new_empty((*lead, world * Kc)) if return_A else None
+        return A_ret, [o.view(*lead, o.shape[-1]) for o in outs]
 
     wsp = symm.get_workspace(group_name, A2.device)
     args = nat.ApkAgGemmArgs()
@@ -460,18 +515,24 @@ def _ag_gemm_last_dim_native(
     args.A_shard = A2.data_ptr()
     args.lda = Kc
     args.A_gathered = stacked.data_ptr() if stacked is not None else None
-    args.return_A = 1 if return_A else 0
+    args.return_A = 1 if (return_A or more) else 0
     args.gather_k = 1
-    for i, (B, out) in enumerate(zip(Bs, outs)):
-        _fill_operand(args.Bs[i], keep, B, out, None, None, None)
+    args.nB = first
+    for i in range(first):
+        _fill_operand(args.Bs[i], keep, Bs[i], outs[i], None, None, None)
     L = nat.lib()
     wsp.ensure(L.apk_ag_gemm_arena_bytes(C.byref(args), world), L.apk_ctrl_bytes(rows, world))
     comm = wsp.next_comm()
     nat.check(L.apk_ag_gemm(C.byref(comm), C.byref(args), _stream_ptr(A2.device)))
-    A_ret = None
-    if return_A:
+    A_cat = None
+    if return_A or more:
         # the reference returns cat(shards, -1) (asynctp_ops.py:663-667); here one strided copy
-        A_ret = stacked.view(world, rows, Kc).permute(1, 0, 2).reshape(*lead, world * Kc)
+        A_cat = stacked.view(world, rows, Kc).permute(1, 0, 2).reshape(rows, world * Kc)
+    for lo in range(first, len(Bs), nat.APK_MAX_B):   # operands beyond one launch's limit: local GEMMs on the gathered A
+        hi = min(lo + nat.APK_MAX_B, len(Bs))
+        none = [None] * (hi - lo)
+        _local_gemm(wsp, A_cat, Bs[lo:hi], outs[lo:hi], None, none, none, none)
+    A_ret = A_cat.view(*lead, world * Kc) if return_A else None
     return A_ret, [o.view(*lead, o.shape[-1]) for o in outs]
 
 
@@ -502,6 +563,8 @@ def _gemm_rs_native(
     A2 = _aligned(A2.contiguous())
     out_shape = (M, B.shape[1] // world) if scatter_cols else (M // world, B.shape[1])
     out = A2.new_empty(out_shape, dtype=out_dtype)
+    if M == 0:
+        return out   # no rows: no collective takes place and the group's epoch does not move
     wsp = symm.get_workspace(group_name, A2.device)
     args = nat.ApkGemmRsArgs()
     keep: list = [A2]
@@ -708,6 +771,8 @@ def _low_contention_all_gather(tensor: torch.Tensor, group_name: str) -> torch.T
     x = _aligned(tensor.contiguous())
     out = x.new_empty((x.shape[0] * world, *x.shape[1:]))
     nbytes = x.numel() * x.element_size()
+    if nbytes == 0:
+        return out
     wsp = symm.get_workspace(group_name, x.device)
     wsp.ensure(nbytes if world > 1 else 0, 256)
     comm = wsp.next_comm()
@@ -729,6 +794,8 @@ def _low_contention_reduce_scatter(tensor: torch.Tensor, reduce_op: str, group_n
     x = _aligned(tensor.contiguous())
     out = x.new_empty((x.shape[0] // world, *x.shape[1:]))
     nbytes = out.numel() * out.element_size()
+    if nbytes == 0:
+        return out
     wsp = symm.get_workspace(group_name, x.device)
     wsp.ensure(nbytes * world if world > 1 else 0, 256)
     comm = wsp.next_comm()

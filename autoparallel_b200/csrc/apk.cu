@@ -20,6 +20,15 @@ namespace {
 thread_local char g_err[512] = "";
 std::atomic<uint64_t> g_launches{0};
 std::atomic<uint64_t> g_pair_launches{0};
+std::atomic<uint64_t> g_pair_refusals{0};
+
+constexpr int kMaxDevices = 64;
+std::mutex g_mu;   // guards every per-device cache below (calls may come from any thread)
+
+// Timeline buffer set by apk_set_trace (device memory of the device that was current then).
+unsigned long long* g_trace = nullptr;
+uint64_t g_trace_bytes = 0;
+int g_trace_device = -1;
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -83,10 +92,11 @@ struct DeviceInfo {
 };
 
 int device_info(DeviceInfo* out) {
-  static DeviceInfo cache[64];
+  static DeviceInfo cache[kMaxDevices];
   int dev = 0;
   APK_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return fail(APK_ERR_ARG, "device index %d out of range", dev);
+  if (dev < 0 || dev >= kMaxDevices) return fail(APK_ERR_ARG, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_mu);
   if (!cache[dev].ok) {
     int major = 0;
     APK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
@@ -99,52 +109,92 @@ int device_info(DeviceInfo* out) {
   return APK_OK;
 }
 
+// Why a device cannot run CTA pairs (empty: it can, or nobody has tried yet). Set once per device, and only
+// when the occupancy query or the launch itself says that clusters of two are not schedulable.
+char g_pair_unsupported[kMaxDevices][160] = {};
+
 template <int BN, int STAGES, bool FP8, bool PAIR>
-int launch_instance(const apk::KParams& kp, long long units, const DeviceInfo& di, cudaStream_t stream) {
+int launch_instance(apk::KParams kp, long long units, const DeviceInfo& di, cudaStream_t stream) {
   using L = apk::SmemLayout<BN, STAGES, PAIR>;
   auto kern = apk::gemm_fused_kernel<BN, STAGES, FP8, PAIR>;
-  static bool configured[64] = {};
-  static int max_clusters[64] = {};
+  static bool configured[kMaxDevices] = {};
+  static int max_clusters[kMaxDevices] = {};
   int dev = 0;
   APK_CUDA(cudaGetDevice(&dev));
-  if (!configured[dev]) {
-    APK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-    configured[dev] = true;
-  }
+  if (dev < 0 || dev >= kMaxDevices) return fail(APK_ERR_ARG, "device index %d out of range", dev);
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(apk::NUM_THREADS);
   cfg.dynamicSmemBytes = L::TOTAL;
   cfg.stream = stream;
-  // Cooperative: all CTAs must be resident at once, because the communication warps of every
-  // CTA feed row blocks that other CTAs' producers wait for.
+  // Cooperative whenever the group has peers: all CTAs must be resident at once, because the
+  // communication warps of every CTA feed row blocks that other CTAs' producers wait for. With a
+  // group of one no CTA waits for another (the two CTAs of a pair are co-scheduled by the cluster
+  // launch itself), so a plain launch does.
   cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeCooperative;
-  attr[0].val.cooperative = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  if (PAIR) {
-    attr[1].id = cudaLaunchAttributeClusterDimension;
-    attr[1].val.clusterDim.x = 2;
-    attr[1].val.clusterDim.y = 1;
-    attr[1].val.clusterDim.z = 1;
-    cfg.numAttrs = 2;
-    if (max_clusters[dev] == 0) {
-      cfg.gridDim = dim3((unsigned)(di.sms & ~1));
-      int n = 0;
-      cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
-      if (e != cudaSuccess || n < 1) {
-        cudaGetLastError();
-        return fail(APK_ERR_CUDA, "CTA pairs cannot be scheduled on this device (%s)", cudaGetErrorString(e));
-      }
-      max_clusters[dev] = n;
-      if (getenv("APK_VERBOSE") != nullptr) fprintf(stderr, "[apk] device %d: %d SMs, at most %d co-resident CTA pairs\n", dev, di.sms, n);
+  int na = 0;
+  if (kp.ws > 1) {
+    attr[na].id = cudaLaunchAttributeCooperative;
+    attr[na].val.cooperative = 1;
+    ++na;
+  }
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!configured[dev]) {
+      APK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+      configured[dev] = true;
     }
+    if (PAIR) {
+      attr[na].id = cudaLaunchAttributeClusterDimension;
+      attr[na].val.clusterDim.x = 2;
+      attr[na].val.clusterDim.y = 1;
+      attr[na].val.clusterDim.z = 1;
+      ++na;
+      cfg.attrs = attr;
+      cfg.numAttrs = na;
+      if (max_clusters[dev] == 0) {
+        cfg.gridDim = dim3((unsigned)(di.sms & ~1));
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+        if (e != cudaSuccess || n < 1) {
+          cudaGetLastError();
+          snprintf(g_pair_unsupported[dev], sizeof(g_pair_unsupported[dev]), "cudaOccupancyMaxActiveClusters: %s, %d clusters",
+                   cudaGetErrorString(e), n);
+          return fail(APK_ERR_CUDA, "CTA pairs cannot be scheduled on device %d (%s)", dev, g_pair_unsupported[dev]);
+        }
+        max_clusters[dev] = n;
+        if (getenv("APK_VERBOSE") != nullptr) fprintf(stderr, "[apk] device %d: %d SMs, at most %d co-resident CTA pairs\n", dev, di.sms, n);
+      }
+    }
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  if (PAIR) {
     const long long clusters = units < max_clusters[dev] ? units : max_clusters[dev];
     cfg.gridDim = dim3((unsigned)(2 * clusters));
   } else {
     cfg.gridDim = dim3((unsigned)(units < di.sms ? units : di.sms));
   }
-  APK_CUDA(cudaLaunchKernelEx(&cfg, kern, kp));
+  // Timeline: one record per (CTA, local tile), only when the buffer set by apk_set_trace is large enough.
+  kp.trace = nullptr;
+  kp.trace_tiles = 0;
+  if (g_trace != nullptr && g_trace_device == dev) {
+    const long long sched_ctas = PAIR ? cfg.gridDim.x / 2 : cfg.gridDim.x;
+    const long long per_cta = (units + sched_ctas - 1) / sched_ctas;
+    const uint64_t need = (uint64_t)cfg.gridDim.x * (uint64_t)per_cta * apk::TRACE_FIELDS * 8;
+    if (need <= g_trace_bytes) {
+      kp.trace = g_trace;
+      kp.trace_tiles = (int32_t)per_cta;
+    }
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, kp);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    if (PAIR && (e == cudaErrorCooperativeLaunchTooLarge || e == cudaErrorNotSupported || e == cudaErrorInvalidClusterSize)) {
+      std::lock_guard<std::mutex> lk(g_mu);
+      snprintf(g_pair_unsupported[dev], sizeof(g_pair_unsupported[dev]), "cluster launch: %s", cudaGetErrorString(e));
+    }
+    return fail(APK_ERR_CUDA, "launch of gemm_fused_kernel<%d,%d,%d,%d>: %s", BN, STAGES, (int)FP8, (int)PAIR, cudaGetErrorString(e));
+  }
   g_launches.fetch_add(1);
   if (PAIR) g_pair_launches.fetch_add(1);
   return APK_OK;
@@ -153,12 +203,13 @@ int launch_instance(const apk::KParams& kp, long long units, const DeviceInfo& d
 // CTA pairs (cta_group::2) are used when every output is a whole number of 256-column tiles and every
 // chunk a whole number of 256-row tile pairs; APK_PAIR=0 in the environment turns them off.
 bool pair_eligible(const apk::KParams& kp) {
-  static int env = -1;
-  if (env < 0) {
+  static std::once_flag once;
+  static bool env_on = true;
+  std::call_once(once, [] {
     const char* e = getenv("APK_PAIR");
-    env = (e != nullptr && e[0] == '0') ? 0 : 1;
-  }
-  if (!env) return false;
+    env_on = !(e != nullptr && e[0] == '0');
+  });
+  if (!env_on) return false;
   for (int b = 0; b < kp.nB; ++b) {
     if (kp.N[b] % 256 != 0) return false;
   }
@@ -175,17 +226,30 @@ int launch(const apk::KParams& kp, int max_n, bool fp8, cudaStream_t stream) {
   long long nt = 0;
   for (int b = 0; b < kp.nB; ++b) nt += (kp.N[b] + bn - 1) / bn;
   const long long mt = (kp.rows_per_rank + apk::BM - 1) / apk::BM;
-  const long long chunks = kp.mode == apk::MODE_PLAIN ? 1 : kp.ws;
+  const long long chunks = (kp.mode == apk::MODE_PLAIN || kp.ag_ksplit) ? 1 : kp.ws;
   const long long tiles = nt * mt * chunks;
   if (tiles <= 0) return APK_OK;
   if (tiles > 0x7fffffffLL) return fail(APK_ERR_ARG, "too many tiles");
-  static bool pair_failed = false;
-  if (!narrow && !pair_failed && pair_eligible(kp)) {
-    rc = fp8 ? launch_instance<256, 6, true, true>(kp, tiles / 2, di, stream)
-             : launch_instance<256, 6, false, true>(kp, tiles / 2, di, stream);
-    if (rc == APK_OK) return rc;
-    pair_failed = true;   // e.g. cooperative cluster launches unsupported: use single CTAs from now on
-    cudaGetLastError();
+  int dev = 0;
+  APK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(APK_ERR_ARG, "device index %d out of range", dev);
+  bool pair_ok;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    pair_ok = g_pair_unsupported[dev][0] == '\0';
+  }
+  if (!narrow && pair_eligible(kp)) {
+    if (pair_ok) {
+      rc = fp8 ? launch_instance<256, 6, true, true>(kp, tiles / 2, di, stream)
+               : launch_instance<256, 6, false, true>(kp, tiles / 2, di, stream);
+      bool unsupported;
+      {
+        std::lock_guard<std::mutex> lk(g_mu);
+        unsupported = g_pair_unsupported[dev][0] != '\0';
+      }
+      if (rc == APK_OK || !unsupported) return rc;   // any other failure is the caller's to see
+    }
+    g_pair_refusals.fetch_add(1);   // this device cannot run pairs: single CTAs, and the count says so
   }
   if (narrow) {
     return fp8 ? launch_instance<128, 6, true, false>(kp, tiles, di, stream) : launch_instance<128, 6, false, false>(kp, tiles, di, stream);
@@ -285,6 +349,18 @@ int apk_abi_version(void) { return APK_ABI_VERSION; }
 const char* apk_last_error(void) { return g_err; }
 uint64_t apk_launch_count(void) { return g_launches.load(); }
 uint64_t apk_pair_launch_count(void) { return g_pair_launches.load(); }
+uint64_t apk_pair_refusal_count(void) { return g_pair_refusals.load(); }
+
+int apk_set_trace(void* buf, uint64_t bytes) {
+  int dev = 0;
+  APK_CUDA(cudaGetDevice(&dev));
+  if (buf != nullptr && (reinterpret_cast<uintptr_t>(buf) & 7u) != 0) return fail(APK_ERR_ARG, "apk_set_trace: buffer must be 8-byte aligned");
+  std::lock_guard<std::mutex> lk(g_mu);
+  g_trace = reinterpret_cast<unsigned long long*>(buf);
+  g_trace_bytes = buf != nullptr ? bytes : 0;
+  g_trace_device = buf != nullptr ? dev : -1;
+  return APK_OK;
+}
 
 int apk_symm_alloc(uint64_t bytes, void** ptr) {
   if (ptr == nullptr || bytes == 0) return fail(APK_ERR_ARG, "apk_symm_alloc: bad arguments");
@@ -393,6 +469,9 @@ int apk_ag_gemm(const apk_comm* comm, const apk_ag_gemm_args* a, void* stream_) 
   if (a->gather_k && (a->dtype != APK_BF16 || a->a_scale_mode != APK_SCALE_NONE))
     return fail(APK_ERR_ARG, "gather_k supports bf16 without scales only");
   if (a->gather_k && (int64_t)a->K * ws > 0x7fffffffLL) return fail(APK_ERR_ARG, "K too large");
+  // K-split: a k-block that runs past a shard's K would multiply A's zero fill with the NEXT rank's rows of B
+  // (0 * Inf = NaN where the reference's cat(A) @ B has none), so every slice must be whole k-blocks.
+  if (a->gather_k && ws > 1 && a->K % 64 != 0) return fail(APK_ERR_ARG, "gather_k needs K (%d) to be a multiple of 64", a->K);
   kp.rows_per_rank = a->rows_per_rank;
   kp.elem_bytes = es;
   int max_n = 0;
@@ -579,6 +658,30 @@ static int coll_common(const apk_comm* comm, uint64_t chunk_bytes, uint64_t aren
   return APK_OK;
 }
 
+// Both collectives release the peers' flags only after a grid-wide count is complete while resident CTAs
+// already spin on the peers' flags, so all CTAs must be co-resident: cooperative launch whenever there are
+// peers, one CTA per SM (the occupancy query caps the grid if the device offers fewer slots).
+static int launch_collective(void (*kern)(const apk::CParams), const apk::CParams& cp, cudaStream_t stream) {
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc != APK_OK) return rc;
+  int per_sm = 0;
+  APK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, apk::COLL_THREADS, 0));
+  if (per_sm < 1) return fail(APK_ERR_CUDA, "the collective kernel does not fit on an SM");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)di.sms);
+  cfg.blockDim = dim3(apk::COLL_THREADS);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = cp.ws > 1 ? 1 : 0;
+  APK_CUDA(cudaLaunchKernelEx(&cfg, kern, cp));
+  g_launches.fetch_add(1);
+  return APK_OK;
+}
+
 int apk_all_gather(const apk_comm* comm, const void* shard, void* out, uint64_t shard_bytes, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (shard_bytes == 0) return APK_OK;
@@ -592,12 +695,7 @@ int apk_all_gather(const apk_comm* comm, const void* shard, void* out, uint64_t 
   cp.flag_stride = apk::FLAG_STRIDE;
   for (int r = 0; r < comm->world && comm->world > 1; ++r) cp.flag_peer[r] = reinterpret_cast<uint32_t*>(comm->flags[r]);
   cp.flag_local = comm->world > 1 ? cp.flag_peer[comm->rank] : nullptr;
-  DeviceInfo di;
-  device_info(&di);
-  apk::all_gather_kernel<<<di.sms, apk::COLL_THREADS, 0, stream>>>(cp);
-  APK_CUDA(cudaGetLastError());
-  g_launches.fetch_add(1);
-  return APK_OK;
+  return launch_collective(apk::all_gather_kernel, cp, stream);
 }
 
 int apk_reduce_scatter(const apk_comm* comm, const void* in, void* out, uint64_t out_bytes, int32_t dtype, int32_t reduce_op, void* stream_) {
@@ -621,12 +719,7 @@ int apk_reduce_scatter(const apk_comm* comm, const void* in, void* out, uint64_t
     for (int r = 0; r < comm->world; ++r) cp.flag_peer[r] = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(comm->flags[r]) + kFlagRsOffset);
     cp.flag_local = cp.flag_peer[comm->rank];
   }
-  DeviceInfo di;
-  device_info(&di);
-  apk::reduce_scatter_kernel<<<di.sms, apk::COLL_THREADS, 0, stream>>>(cp);
-  APK_CUDA(cudaGetLastError());
-  g_launches.fetch_add(1);
-  return APK_OK;
+  return launch_collective(apk::reduce_scatter_kernel, cp, stream);
 }
 
 int apk_debug_schedule(int32_t mode, int32_t world, int32_t rank, int32_t rows_per_rank, int32_t nB, const int32_t* N,

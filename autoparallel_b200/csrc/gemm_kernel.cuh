@@ -109,6 +109,41 @@ struct alignas(64) KParams {
   uint32_t epoch;
   uint32_t* status;
   long long timeout_cycles;
+  // ---- optional timeline (apk_set_trace): TRACE_FIELDS u64 per (CTA, local tile), null when off
+  unsigned long long* trace;
+  int32_t trace_tiles;                 // records per CTA
+};
+
+// Fields of one timeline record. Times are %globaltimer nanoseconds, waits are SM cycles.
+enum TraceField : int {
+  TR_TILE = 0,          // producer: global tile index + 1 (0: record unused)
+  TR_LOAD_T = 1,        // producer: first load of the tile issued
+  TR_READY_WAIT = 2,    // producer: cycles waiting for gathered rows (all-gather mode)
+  TR_EMPTY_WAIT = 3,    // producer: cycles waiting for free pipeline stages
+  TR_MMA_T = 4,         // MMA thread: first MMA of the tile issued
+  TR_FULL_WAIT = 5,     // MMA thread: cycles waiting for operands
+  TR_TEMPTY_WAIT = 6,   // MMA thread: cycles waiting for a free accumulator
+  TR_COMMIT_T = 7,      // MMA thread: the tile's last MMA issued and committed
+  TR_TFULL_T = 8,       // epilogue: accumulator complete
+  TR_PARTIAL_WAIT = 9,  // epilogue: cycles waiting for the peers' partials (reduce-scatter, own tile)
+  TR_EPI_END_T = 10,    // epilogue: the tile's stores issued
+  TR_PUBLISH = 11,      // epilogue: cycles inside flag publication during this tile
+  TR_FLAGS_T = 12,      // summing warps: all peers' flags of an own tile acquired
+  TR_SUMS_T = 13,       // summing warps: sums of an own tile written
+  TR_CTA_BEGIN_T = 14,  // record 0 of a CTA: CTA start in ns; record 1: the same instant in SM cycles
+  TR_CTA_END_T = 15,    // record 0: CTA end in ns; record 1: in SM cycles (cycles / ns = the SM clock in GHz)
+  TRACE_FIELDS = 16
+};
+
+// Pipeline stages are handed back to the producer in groups of RELEASE_EVERY k-blocks (one
+// tcgen05.commit per group instead of one per k-block). The single MMA-issuing thread is the
+// scarce resource of this kernel: measured on B200, a tcgen05.mma (cta_group::2) costs it about 75
+// cycles, a commit 140-170 and a barrier wait 55-85, against 128 tensor-pipe cycles per 256 x 256 x 16
+// MMA; with four MMAs per commit and wait the thread, not the pipe, sets the pace (about 690 cycles
+// per k-block against 512), with eight it stays ahead of the pipe.
+template <int STAGES>
+struct ReleaseEvery {
+  static constexpr int value = (STAGES % 2 == 0 && STAGES >= 6) ? 2 : 1;
 };
 
 template <int BN, int STAGES, bool PAIR = false>
@@ -247,6 +282,21 @@ __device__ __forceinline__ int ag_tile_pieces(const KParams& p, int mt) {
   long long len = p.ag_chunk_bytes - start;
   if (len > tile_bytes) len = tile_bytes;
   return (int)((len + PIECE_BYTES - 1) / PIECE_BYTES);
+}
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Timeline slot `field` of this CTA's local tile `lt`; null when tracing is off or the buffer is full.
+__device__ __forceinline__ unsigned long long* trace_slot(const KParams& p, uint32_t lt, int field) {
+  if (p.trace == nullptr || lt >= (uint32_t)p.trace_tiles) return nullptr;
+  return p.trace + ((size_t)blockIdx.x * p.trace_tiles + lt) * TRACE_FIELDS + field;
+}
+__device__ __forceinline__ void trace_put(const KParams& p, uint32_t lt, int field, unsigned long long v) {
+  unsigned long long* s = trace_slot(p, lt, field);
+  if (s != nullptr) *s = v;
 }
 
 __device__ __forceinline__ void set_status(const KParams& p, uint32_t code, uint32_t detail) {
@@ -409,6 +459,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
   constexpr int UMMA_K = FP8 ? 32 : 16;         // K elements per tcgen05.mma (32 bytes)
   constexpr int KSTEPS = BKE / UMMA_K;          // 4
   constexpr int NPB = FP8 ? 128 : 64;           // N elements per TMA box when B is N-major
+  constexpr int RE = ReleaseEvery<STAGES>::value;   // k-blocks per stage release
   constexpr uint32_t TMEM_COLS = 2 * BN <= 32 ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
 
   extern __shared__ uint8_t smem_raw[];
@@ -425,6 +476,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
   volatile uint32_t* epi_verdict = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFF + 8);  // [2]
   // reduce-scatter: how many of this CTA's own tiles have had their peers' partials summed
   volatile uint32_t* sums_done = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFF + 16);
+  // reduce-scatter: the summing warps' shared decision to go on (written by one thread per tile)
+  volatile uint32_t* sum_verdict = reinterpret_cast<volatile uint32_t*>(smem + L::MISC_OFF + 20);   // [2]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -470,9 +523,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       if (p.mode == MODE_AG) ptx::tma_prefetch_desc(&p.tmA1);
       for (int b = 0; b < p.nB; ++b) ptx::tma_prefetch_desc(&p.tmB[b]);
       uint32_t it = 0;       // k-block counter over the CTA's lifetime
+      uint32_t pstage = 0, pphase = 0;   // = it % STAGES and (it / STAGES) & 1, kept as counters
+      uint32_t lt = 0;       // local tile counter
+      const bool tracing = p.trace != nullptr;
       bool ok = true;
-      for (int t = tile_first; t < sched.total_tiles && ok; t += tile_step) {
+      if (tracing) {
+        trace_put(p, 0, TR_CTA_BEGIN_T, globaltimer_ns());
+        trace_put(p, 1, TR_CTA_BEGIN_T, (unsigned long long)clock64());
+      }
+      for (int t = tile_first; t < sched.total_tiles && ok; t += tile_step, ++lt) {
         const TileInfo ti = decode_tile<BN, PAIR>(p, sched, t, crank);
+        long long tr_ready = 0, tr_empty = 0;
         const CUtensorMap* tmA = &p.tmA0;
         int arow = ti.mt * BM;
         int bcol = ti.n0;     // first column of B for this tile
@@ -482,8 +543,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
           tmA = &p.tmA1;
           arow += ti.chunk * p.rows_per_rank;
           const uint32_t expect = (uint32_t)ag_tile_pieces(p, ti.mt) + (p.ag_has_scale ? 1u : 0u);
+          const long long c0 = tracing ? clock64() : 0;
           ok = flag_wait<false>(p.ready + ti.chunk * sched.mt_per_chunk + ti.mt, expect, p, abort_flag,
                                 ST_TIMEOUT_READY, (uint32_t)ti.chunk);
+          if (tracing) tr_ready += clock64() - c0;
           if (!ok) break;
           ptx::fence_proxy_async_global();
         } else if (p.mode == MODE_RS) {
@@ -492,8 +555,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
         const bool nmajor = p.b_nmajor[ti.b] != 0;
         const CUtensorMap* tmB = &p.tmB[ti.b];
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
+          const int s = (int)pstage;
+          const uint32_t ph = pphase;
+          if (++pstage == (uint32_t)STAGES) { pstage = 0; pphase ^= 1u; }
           int ka = kb * BKE, kbB = kb * BKE;     // K coordinates in A and in B
           if (p.ag_ksplit) {
             // K-slice of rank (rank + step): own slice first, then the peers' as they arrive
@@ -506,14 +570,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
               arow = ti.mt * BM + ((src == p.rank) ? 0 : src * p.rows_per_rank);
               if (src != p.rank) {
                 const uint32_t expect = (uint32_t)ag_tile_pieces(p, ti.mt);
+                const long long c0 = tracing ? clock64() : 0;
                 ok = flag_wait<false>(p.ready + src * sched.mt_per_chunk + ti.mt, expect, p, abort_flag,
                                       ST_TIMEOUT_READY, (uint32_t)src);
+                if (tracing) tr_ready += clock64() - c0;
                 if (!ok) break;
                 ptx::fence_proxy_async_global();
               }
             }
           }
-          ok = mbar_wait(empty_bar(s), ph ^ 1u, p, abort_flag);
+          {
+            // stages come back in groups of RE: only the first stage of a group waits
+            const long long c0 = tracing ? clock64() : 0;
+            if (s % RE == 0) ok = mbar_wait(empty_bar(s / RE), ph ^ 1u, p, abort_flag);
+            if (tracing) {
+              tr_empty += clock64() - c0;
+              if (kb == 0) {
+                trace_put(p, lt, TR_TILE, (unsigned long long)t + 1ull);
+                trace_put(p, lt, TR_LOAD_T, globaltimer_ns());
+              }
+            }
+          }
           if (!ok) break;
           const uint32_t a_dst = smem_base + s * L::STAGE_BYTES;
           const uint32_t b_dst = a_dst + L::A_BYTES;
@@ -544,6 +621,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
             }
           }
         }
+        if (tracing) {
+          trace_put(p, lt, TR_READY_WAIT, (unsigned long long)tr_ready);
+          trace_put(p, lt, TR_EMPTY_WAIT, (unsigned long long)tr_empty);
+        }
       }
       // Drain: every load this thread armed has either landed or is given a bounded time to.
       const uint32_t last = (PAIR && crank != 0) ? 0u : it;   // (rank 1 of a pair has no full barriers of its own)
@@ -568,14 +649,29 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       // Instruction descriptor: fp32 accumulate, A/B format (bf16 = 1, e4m3 = 0), M = 128.
       const uint32_t fmt = FP8 ? 0u : 1u;
       const uint32_t idesc_base = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t((PAIR ? 2 * BM : BM) >> 4) << 24);
-      uint32_t it = 0;
       uint32_t lt = 0;  // local tile counter
+      const bool tracing = p.trace != nullptr;
       bool ok = true;
+      // The loop below is kept short on purpose (see ReleaseEvery): stage and phase are running counters,
+      // the barrier addresses of both CTAs are computed once, and the next stage's `full` barrier is
+      // probed (non-blocking) before this stage's MMAs are issued, so that its latency is hidden.
+      uint32_t stage = 0, phase = 0;
+      const uint32_t full0 = full_bar(0);
+      const uint32_t empty_c0 = PAIR ? ptx::mapa(empty_bar(0), 0) : empty_bar(0);
+      const uint32_t empty_c1 = PAIR ? ptx::mapa(empty_bar(0), 1) : 0u;
+      const uint32_t a_lo0 = (smem_base >> 4) & 0x3fffu;
+      const uint32_t b_lo0 = ((smem_base + L::A_BYTES) >> 4) & 0x3fffu;
+      bool ready = ptx::mbar_test_wait(full0, 0u);
       for (int t = tile_first; t < sched.total_tiles && ok; t += tile_step, ++lt) {
         const TileInfo ti = decode_tile<BN, PAIR>(p, sched, t, crank);
         const uint32_t acc = lt & 1u;
         const uint32_t aph = (lt >> 1) & 1u;
-        ok = mbar_wait(tempty_bar(acc), aph ^ 1u, p, abort_flag);
+        long long tr_full = 0;
+        {
+          const long long c0 = tracing ? clock64() : 0;
+          ok = mbar_wait(tempty_bar(acc), aph ^ 1u, p, abort_flag);
+          if (tracing) trace_put(p, lt, TR_TEMPTY_WAIT, (unsigned long long)(clock64() - c0));
+        }
         if (!ok) break;
         ptx::tc_fence_after();
         const bool nmajor = p.b_nmajor[ti.b] != 0;
@@ -584,16 +680,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
         const uint32_t d_tmem = tmem_base + acc * BN;
         const uint64_t bdesc_hi = nmajor ? desc_nmajor : desc_kmajor;
         const uint32_t bstep = nmajor ? uint32_t((UMMA_K * ROW_BYTES) >> 4) : 2u;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
-          ok = mbar_wait(full_bar(s), ph, p, abort_flag);
-          if (!ok) break;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ready) {
+            const long long c0 = tracing ? clock64() : 0;
+            ok = mbar_wait(full0 + 8u * stage, phase, p, abort_flag);
+            if (tracing) tr_full += clock64() - c0;
+            if (!ok) break;
+          }
+          if (tracing && kb == 0) trace_put(p, lt, TR_MMA_T, globaltimer_ns());
           ptx::tc_fence_after();
-          const uint32_t a_addr = smem_base + s * L::STAGE_BYTES;
-          const uint32_t b_addr = a_addr + L::A_BYTES;
-          const uint64_t adesc = desc_kmajor | uint64_t((a_addr >> 4) & 0x3fffu);
-          const uint64_t bdesc = bdesc_hi | uint64_t((b_addr >> 4) & 0x3fffu);
+          const uint32_t s = stage;
+          if (++stage == (uint32_t)STAGES) { stage = 0; phase ^= 1u; }
+          ready = ptx::mbar_test_wait(full0 + 8u * stage, phase);   // the NEXT k-block's operands (may belong to the next tile)
+          const uint64_t adesc = desc_kmajor | uint64_t(a_lo0 + s * (uint32_t)(L::STAGE_BYTES >> 4));
+          const uint64_t bdesc = bdesc_hi | uint64_t(b_lo0 + s * (uint32_t)(L::STAGE_BYTES >> 4));
 #pragma unroll
           for (int k = 0; k < KSTEPS; ++k) {
             const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
@@ -606,11 +706,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
               ptx::mma_f16(d_tmem, adesc + 2u * k, bdesc + bstep * k, idesc, accum);
             }
           }
-          if (PAIR) {   // the stage is free again in both CTAs
-            ptx::tc_commit_pair(ptx::mapa(empty_bar(s), 0));
-            ptx::tc_commit_pair(ptx::mapa(empty_bar(s), 1));
-          } else {
-            ptx::tc_commit(empty_bar(s));
+          if (s % RE == RE - 1) {   // the group of stages is free again (in both CTAs of a pair)
+            if (PAIR) {
+              ptx::tc_commit_pair(empty_c0 + 8u * (s / RE));
+              ptx::tc_commit_pair(empty_c1 + 8u * (s / RE));
+            } else {
+              ptx::tc_commit(empty_c0 + 8u * (s / RE));
+            }
           }
         }
         if (ok) {
@@ -620,6 +722,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
           } else {
             ptx::tc_commit(tfull_bar(acc));
           }
+        }
+        if (tracing) {
+          trace_put(p, lt, TR_FULL_WAIT, (unsigned long long)tr_full);
+          trace_put(p, lt, TR_COMMIT_T, globaltimer_ns());
         }
       }
       // Make sure nothing this thread issued is still running before TMEM is freed.
@@ -636,6 +742,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
     const bool epi_leader = (warp == 2 && lane == 0);
     const uint32_t stg_base = smem_base + L::STG_OFF + (warp - 2) * L::STG_WARP_BYTES;
     uint32_t stg_count = 0;
+    uint32_t lt = 0;
+    const bool tracing = p.trace != nullptr;
     // Reduce-scatter: tiles sent to their owners and not yet announced, oldest first (the same
     // values in all 4 warps). Up to four tiles stay in flight and flags are released two tiles at
     // a time behind ONE system-scope fence: a fence costs a round trip over a busy NVLink, so it
@@ -649,6 +757,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       // groups; direct stores: each thread's own, fenced by itself), then the flags
       const int newer = pq_newer[count - 1];
       bool generic = pq_gen[0] || (count == 2 && pq_gen[1]);
+      const long long c0 = (tracing && epi_leader) ? clock64() : 0;
       if (lane == 0) ptx::bulk_wait_group_upto(newer);
       if (generic) __threadfence_system();
       ptx::named_bar_sync(2, EPI_WARPS * 32);
@@ -656,6 +765,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
         __threadfence_system();
         ptx::st_relaxed_sys(pq_flag[0], p.epoch);
         if (count == 2) ptx::st_relaxed_sys(pq_flag[1], p.epoch);
+        if (tracing) {
+          unsigned long long* slot = trace_slot(p, lt, TR_PUBLISH);
+          if (slot != nullptr) *slot += (unsigned long long)(clock64() - c0);
+        }
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -682,7 +795,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       ++pq_n;
     };
     uint32_t own_seen = 0;   // own reduce-scatter tiles this CTA has finished
-    uint32_t lt = 0;
     for (int t = tile_first; t < sched.total_tiles; t += tile_step, ++lt) {
       const TileInfo ti = decode_tile<BN, PAIR>(p, sched, t, crank);
       const uint32_t acc = lt & 1u;
@@ -700,6 +812,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       // accumulator); its verdict is shared so that all four warps leave the loop together.
       if (epi_leader) {
         bool good = true;
+        const long long c0 = tracing ? clock64() : 0;
         if (p.mode == MODE_RS && own && p.ws > 1 && p.rs_arena_tma != 0) {
           // the communication warps acquire the peers' flags and leave the sum of their partials
           good = smem_count_wait(sums_done, own_seen + 1u, p, abort_flag);
@@ -710,7 +823,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
                                    abort_flag, ST_TIMEOUT_PARTIAL, (uint32_t)src);
           }
         }
+        if (tracing) trace_put(p, lt, TR_PARTIAL_WAIT, (unsigned long long)(clock64() - c0));
         if (good) good = mbar_wait(tfull_bar(acc), aph, p, abort_flag);
+        if (tracing) trace_put(p, lt, TR_TFULL_T, globaltimer_ns());
         epi_verdict[lt & 1u] = good ? 1u : 0u;
       }
       ptx::named_bar_sync(1, EPI_WARPS * 32);
@@ -918,6 +1033,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       if (lane == 0) {
         if (PAIR) ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(acc), 0)); else ptx::mbar_arrive(tempty_bar(acc));
       }
+      if (tracing && epi_leader) trace_put(p, lt, TR_EPI_END_T, globaltimer_ns());
 
       if (p.mode == MODE_RS && own) ++own_seen;
       if (rs_remote) {
@@ -939,21 +1055,26 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       const int cw = warp - (2 + EPI_WARPS);
       const size_t src_stride = (size_t)sched.tiles_per_chunk * (BN / 64) * 4 * (32 * ROW_BYTES);
       uint32_t done = 0;
-      bool ok = true;
-      for (int t = tile_first; t < sched.total_tiles && ok; t += tile_step) {
+      uint32_t lt = 0;
+      const bool tracing = p.trace != nullptr;
+      for (int t = tile_first; t < sched.total_tiles; t += tile_step, ++lt) {
         const TileInfo ti = decode_tile<BN, PAIR>(p, sched, t, crank);
         if (ti.chunk != p.rank) continue;
-        if (cw == 0) {
-          if (lane == 0) {
-            for (int src = 0; src < p.ws && ok; ++src) {
-              if (src == p.rank) continue;
-              ok = flag_wait<true>(p.rs_flag_local + (size_t)src * p.rs_max_tiles + ti.tile_in_chunk, p.epoch, p,
-                                   abort_flag, ST_TIMEOUT_PARTIAL, (uint32_t)src);
-            }
+        // One thread waits for the peers' flags; its verdict (which also covers an abort raised by
+        // another role) goes through shared memory, so that all six warps take the same branch.
+        if (cw == 0 && lane == 0) {
+          bool ok = true;
+          for (int src = 0; src < p.ws && ok; ++src) {
+            if (src == p.rank) continue;
+            ok = flag_wait<true>(p.rs_flag_local + (size_t)src * p.rs_max_tiles + ti.tile_in_chunk, p.epoch, p,
+                                 abort_flag, ST_TIMEOUT_PARTIAL, (uint32_t)src);
           }
+          if (*abort_flag) ok = false;
+          sum_verdict[done & 1u] = ok ? 1u : 0u;
+          if (tracing) trace_put(p, lt, TR_FLAGS_T, globaltimer_ns());
         }
         ptx::named_bar_sync(3, COMM_WARPS * 32);
-        if (*abort_flag) break;
+        if (sum_verdict[done & 1u] == 0u) break;
         const int groups = (ti.n_valid + 63) / 64;
         for (int blk16 = cw; blk16 < groups * 4; blk16 += COMM_WARPS) {
           const size_t blk = ((size_t)ti.tile_in_chunk * (BN / 64) * 4 + blk16);
@@ -998,7 +1119,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
         __threadfence();
         ptx::named_bar_sync(3, COMM_WARPS * 32);
         ++done;
-        if (cw == 0 && lane == 0) *sums_done = done;
+        if (cw == 0 && lane == 0) {
+          *sums_done = done;
+          if (tracing) trace_put(p, lt, TR_SUMS_T, globaltimer_ns());
+        }
       }
     }
     if (p.mode == MODE_AG) {
@@ -1124,6 +1248,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
   // ============================================================ teardown
   ptx::tc_fence_before();
   if (PAIR) ptx::cluster_sync(); else __syncthreads();   // pair: nobody signals a CTA that has left
+  if (threadIdx.x == 0 && p.trace != nullptr) {
+    trace_put(p, 0, TR_CTA_END_T, globaltimer_ns());
+    trace_put(p, 1, TR_CTA_END_T, (unsigned long long)clock64());
+  }
   if (warp == 1) {
     ptx::tc_fence_after();
     if (PAIR) ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS); else ptx::tmem_dealloc(tmem_base, TMEM_COLS);

@@ -14,7 +14,14 @@ Protocol facts the kernels rely on (kept here because this module owns ``epoch``
   for a signal that every other rank produces during the same op, so a rank that has reached
   op ``e + 2`` knows that all peers have finished op ``e`` and may overwrite that half;
 * flags carry epoch values and are compared with ``>=`` (wrap-safe), so they are never reset;
-  when the arena grows, the new signal pad is zero and the epoch restarts from zero with it.
+  when the arena grows, the new signal pad is zero and the epoch restarts from zero with it;
+* the epoch reaches the kernel by value, so a collective op must not be recorded into a CUDA
+  graph: a replay would carry the recorded epoch, every flag would already satisfy
+  ``flag >= epoch`` and the kernel would read data the peers have not written yet.
+  ``next_comm()`` therefore refuses to run during stream capture when the group has peers
+  (the reference's barriers, autoparallel/asynctp_ops.py:65, :147, are replay-safe; this
+  protocol is not, and says so instead of computing garbage). A group of one rank has no
+  flags and may be captured.
 """
 from __future__ import annotations
 
@@ -29,6 +36,11 @@ from . import _native as nat
 
 FLAG_PAD_BYTES = 4096 + 4 * nat.APK_MAX_WORLD * 65536  # staged flags + 65536 tile flags per source rank
 DEFAULT_TIMEOUT_S = 30.0
+
+
+def _capturing() -> bool:
+    """True while the current CUDA stream records a graph (False on a machine without CUDA)."""
+    return torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()
 
 
 def _round_up(x: int, a: int) -> int:
@@ -108,7 +120,7 @@ class GroupWorkspace:
         need = 2 * _round_up(half_bytes, 4096)
         if need <= self.handles.data_bytes and self._local_flags:
             return
-        if torch.cuda.is_current_stream_capturing():
+        if _capturing():
             raise RuntimeError("the symmetric workspace cannot grow during CUDA graph capture")
         L = nat.lib()
         # Nobody may still be reading the old arena: drain the device, then meet the peers.
@@ -136,6 +148,12 @@ class GroupWorkspace:
     # ------------------------------------------------------------------ per call
     def next_comm(self) -> nat.ApkComm:
         """The comm descriptor of the next collective op (advances the epoch)."""
+        if self.world > 1 and _capturing():
+            raise RuntimeError(
+                "the fused async-TP ops cannot be captured into a CUDA graph when the group has peers: the "
+                "flag epoch is passed by value and a replay would reuse it (run them outside the graph, "
+                "e.g. torch._inductor.config.triton.cudagraphs = False)"
+            )
         self.epoch = (self.epoch + 1) & 0xFFFFFFFF
         c = nat.ApkComm()
         c.rank = self.rank
@@ -145,6 +163,19 @@ class GroupWorkspace:
             c.flags[r] = self.handles.flags[r]
         c.data_bytes = self.handles.data_bytes
         c.flag_bytes = self.handles.flag_bytes
+        c.ctrl = self.ctrl.data_ptr()
+        c.ctrl_bytes = self.ctrl.numel() * 4
+        c.status = self.status.data_ptr()
+        c.epoch = self.epoch
+        c.timeout_s = self.timeout_s
+        return c
+
+    def local_comm(self) -> nat.ApkComm:
+        """A descriptor for work on this rank alone (a group of one): no peers, no flags, and the
+        group's epoch does not move."""
+        c = nat.ApkComm()
+        c.rank = 0
+        c.world = 1
         c.ctrl = self.ctrl.data_ptr()
         c.ctrl_bytes = self.ctrl.numel() * 4
         c.status = self.status.data_ptr()

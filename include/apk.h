@@ -216,6 +216,26 @@ int apk_debug_schedule(int32_t mode, int32_t world, int32_t rank, int32_t rows_p
 uint64_t apk_launch_count(void);
 /* ... of which launched as clusters of two CTAs (tcgen05 cta_group::2). */
 uint64_t apk_pair_launch_count(void);
+/* Calls whose shape qualified for CTA pairs but ran on single CTAs because the device cannot schedule
+ * clusters of two (the reason is in apk_last_error() of the first such call). 0 on a healthy B200. */
+uint64_t apk_pair_refusal_count(void);
+
+/*
+ * Timeline of the fused kernel, for profiling (the reference wraps each op in
+ * torch.profiler.record_function, autoparallel/asynctp_ops.py:741, :1077; a single kernel needs
+ * stamps from inside). While `buf` (device memory of the current device, zero-filled by the
+ * caller, `bytes` long) is set, every apk_ag_gemm / apk_gemm_rs launch on that device whose
+ * records fit writes 16 u64 per (CTA, local tile): record index = blockIdx * tiles_per_cta +
+ * local tile, tiles_per_cta = ceil(scheduling units / scheduled CTAs or CTA pairs). Fields, in
+ * order: tile index + 1; first load issued (ns, %globaltimer); producer cycles waiting for
+ * gathered rows; for free stages; first MMA issued (ns); MMA-thread cycles waiting for
+ * operands; for a free accumulator; last MMA committed (ns); accumulator complete (ns);
+ * epilogue cycles waiting for peers' partials; epilogue done (ns); cycles spent publishing
+ * flags; peers' flags of an own tile acquired (ns); their sums written (ns); CTA begin and
+ * end (ns, record 0 of each CTA only). Pass null to switch it off. Not thread-safe against
+ * concurrent launches; costs one predictable branch per stamp when off.
+ */
+int apk_set_trace(void* buf, uint64_t bytes);
 
 #ifdef __cplusplus
 }

@@ -139,3 +139,49 @@ def test_scaled_reduce_scatter_marshalling(recorder):
         ops._fused_scaled_matmul_reduce_scatter(
             A, B, torch.ones(3, 32, 1), torch.ones(1, 48), "sum", 1, 1, g, [2, 32, 48], None, None, torch.bfloat16, False
         )
+
+
+def test_more_operands_than_one_launch_takes(recorder):
+    """Six Bs (the reference takes any number, autoparallel/asynctp_ops.py:445-454): one fused launch
+    for the first four that also leaves the whole gathered A behind, then a local launch (a group of
+    one, no epoch) for the rest on that gathered A."""
+    rec, g = recorder
+    bf = torch.bfloat16
+    A = torch.zeros(16, 64, dtype=bf)
+    Bs = [torch.zeros(64, 8 * (i + 1), dtype=bf) for i in range(6)]
+    n = [None] * 6
+    A_out, outs = ops._ag_gemm_native(A, Bs, None, n, n, n, [bf] * 6, 0, g, False)
+    (c0, a0), (c1, a1) = rec.ag
+    assert A_out is None and [tuple(o.shape) for o in outs] == [(128, 8 * (i + 1)) for i in range(6)]
+    assert (c0.world, c0.epoch, a0.nB, a0.rows_per_rank, a0.return_A) == (8, 1, 4, 16, 1)
+    assert (c1.world, c1.rank, a1.nB, a1.rows_per_rank, a1.K) == (1, 0, 2, 128, 64)
+    assert a1.A_shard == a0.A_gathered and [a1.Bs[i].N for i in range(2)] == [40, 48]
+    assert symm.get_workspace(g, A.device).epoch == 1            # the local launch is not a collective
+
+
+def test_more_operands_with_row_scales(recorder):
+    rec, g = recorder
+    f8 = torch.float8_e4m3fn
+    A = torch.zeros(16, 32, dtype=f8)
+    Bs = [torch.zeros(24, 32, dtype=f8).t() for _ in range(5)]
+    ops._fused_all_gather_scaled_matmul(A, Bs, torch.ones(16, 1), [torch.ones(1, 24)] * 5, 0, g, [None] * 5, [None] * 5,
+                                        [torch.bfloat16] * 5, [False] * 5)
+    (_, a0), (c1, a1) = rec.ag
+    assert (a0.nB, a0.a_scale_mode) == (4, nat.APK_SCALE_VECTOR)
+    # the second launch sees one scale per row of the gathered A: the peers' rows gathered by the kernel, own rows copied in
+    assert (c1.world, a1.nB, a1.a_scale_mode, a1.rows_per_rank) == (1, 1, nat.APK_SCALE_ROWS_REPLICATED, 128)
+    assert a1.A_scale == a0.A_scale_gathered
+
+
+def test_empty_inputs_are_not_collectives(recorder):
+    """No rows: nothing is launched and the group's epoch does not move (an op that advanced it
+    without waiting for its peers would break the arena's two-op reuse distance)."""
+    rec, g = recorder
+    bf = torch.bfloat16
+    A_out, (o,) = ops._ag_gemm_native(torch.zeros(0, 64, dtype=bf), [torch.zeros(64, 8, dtype=bf)], None, [None], [None],
+                                      [None], [bf], 0, g, True)
+    assert tuple(A_out.shape) == (0, 64) and tuple(o.shape) == (0, 8)
+    out = ops._fused_matmul_reduce_scatter(torch.zeros(0, 64, dtype=bf), torch.zeros(64, 8, dtype=bf), "sum", 0, g)
+    assert tuple(out.shape) == (0, 8)
+    assert not rec.ag and not rec.rs
+    assert g not in symm._workspaces or symm._workspaces[g].epoch == 0

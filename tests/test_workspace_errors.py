@@ -66,10 +66,25 @@ def group(monkeypatch):
 def test_growth_is_refused_during_graph_capture(group, monkeypatch):
     fake, g = group
     w = symm.get_workspace(g, torch.device("cpu"))
-    monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: True)
+    monkeypatch.setattr(symm, "_capturing", lambda: True)
     with pytest.raises(RuntimeError, match="cannot grow during CUDA graph capture"):
         w.ensure(1 << 20, 256)
     assert not fake.live          # nothing was allocated or exchanged
+
+
+def test_ops_with_peers_refuse_graph_capture(group, monkeypatch):
+    """The epoch travels by value, so a replayed graph would satisfy every flag at once and read data the
+    peers have not written: next_comm() refuses during capture and leaves the epoch where it was."""
+    fake, g = group
+    w = symm.get_workspace(g, torch.device("cpu"))
+    w.next_comm()
+    before = w.epoch
+    monkeypatch.setattr(symm, "_capturing", lambda: True)
+    with pytest.raises(RuntimeError, match="cannot be captured into a CUDA graph"):
+        w.next_comm()
+    assert w.epoch == before
+    c = w.local_comm()                    # work on this rank alone has no flags and may be captured
+    assert (c.world, c.rank, c.epoch) == (1, 0, before) and w.epoch == before
 
 
 def test_single_rank_group_needs_no_arena(monkeypatch):
