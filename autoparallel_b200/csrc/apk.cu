@@ -217,7 +217,23 @@ bool pair_eligible(const apk::KParams& kp) {
   return mt % 2 == 0;
 }
 
-int launch(const apk::KParams& kp, int max_n, bool fp8, cudaStream_t stream) {
+// Reduce-scatter: how many row blocks the own tiles trail the peers' (KParams::rs_lag). Two needs, both
+// in units of grid waves (measured at 8 ranks: a partial is acknowledged about 10 us after it was sent and
+// announced about 8 us later, a tile takes about 14 us): a peer's partial for row block j must be there
+// before the owner's epilogue asks for it, so row block j of the own chunk follows about three waves behind
+// the peers' row block j; and the own tiles that remain after the last partial was sent should keep the
+// tensor pipe busy for two to three waves while that partial crosses NVLink and is summed.
+int rs_lag_for(const apk::KParams& kp, long long nt, long long sched_ctas) {
+  const long long per_row_block = nt * (kp.ws - 1);   // peers' units per row block
+  if (per_row_block <= 0 || nt <= 0) return apk::RS_LAG;
+  const long long head = (3 * sched_ctas + per_row_block - 1) / per_row_block;
+  const long long tail = (5 * sched_ctas / 2 + nt - 1) / nt;
+  const long long want = head > tail ? head : tail;
+  return (int)(want > apk::RS_LAG ? want : apk::RS_LAG);
+}
+
+int launch(const apk::KParams& kp_in, int max_n, bool fp8, cudaStream_t stream) {
+  apk::KParams kp = kp_in;
   DeviceInfo di;
   int rc = device_info(&di);
   if (rc != APK_OK) return rc;
@@ -238,8 +254,10 @@ int launch(const apk::KParams& kp, int max_n, bool fp8, cudaStream_t stream) {
     std::lock_guard<std::mutex> lk(g_mu);
     pair_ok = g_pair_unsupported[dev][0] == '\0';
   }
+  if (kp.mode == apk::MODE_RS && kp.ws > 1) kp.rs_lag = rs_lag_for(kp, nt, di.sms);
   if (!narrow && pair_eligible(kp)) {
     if (pair_ok) {
+      if (kp.mode == apk::MODE_RS && kp.ws > 1) kp.rs_lag = rs_lag_for(kp, nt, di.sms / 2);
       rc = fp8 ? launch_instance<256, 6, true, true>(kp, tiles / 2, di, stream)
                : launch_instance<256, 6, false, true>(kp, tiles / 2, di, stream);
       bool unsupported;
@@ -250,6 +268,7 @@ int launch(const apk::KParams& kp, int max_n, bool fp8, cudaStream_t stream) {
       if (rc == APK_OK || !unsupported) return rc;   // any other failure is the caller's to see
     }
     g_pair_refusals.fetch_add(1);   // this device cannot run pairs: single CTAs, and the count says so
+    if (kp.mode == apk::MODE_RS && kp.ws > 1) kp.rs_lag = rs_lag_for(kp, nt, di.sms);
   }
   if (narrow) {
     return fp8 ? launch_instance<128, 6, true, false>(kp, tiles, di, stream) : launch_instance<128, 6, false, false>(kp, tiles, di, stream);

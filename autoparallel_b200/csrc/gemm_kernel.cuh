@@ -40,7 +40,7 @@ constexpr int EPI_WARPS = 4;
 constexpr int COMM_WARPS = 6;
 constexpr int NUM_THREADS = 32 * (2 + EPI_WARPS + COMM_WARPS);
 constexpr int PIECE_BYTES = 4096;   // unit of the all-gather pull: 32 lanes x 16 B x 8
-constexpr int RS_LAG = 4;          // reduce-scatter: own row block j is scheduled this many row blocks after the peers' j
+constexpr int RS_LAG = 4;          // reduce-scatter: default distance (row blocks) between the peers' row block j and the own one
 constexpr int FLAG_STRIDE = 32;     // u32 words between two ranks' "staged" flags (128 B)
 
 enum Mode : int32_t { MODE_PLAIN = 0, MODE_AG = 1, MODE_RS = 2 };
@@ -104,6 +104,7 @@ struct alignas(64) KParams {
   int32_t rs_max_tiles;
   int32_t rs_slot_rows;                // rows_per_rank rounded up to whole 128-row tiles
   int32_t rs_arena_tma;                // bf16 partials: blocked arena written by bulk copies
+  int32_t rs_lag;                      // own row block j is scheduled this many row blocks after the peers' j (0: RS_LAG)
   float reduce_scale;                  // 1 for sum, 1/ws for avg
   // ---- common
   uint32_t epoch;
@@ -152,8 +153,10 @@ struct SmemLayout {
   static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * ROW_BYTES;   // a CTA of a pair holds half of B's columns
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STG_OFF = STAGES * STAGE_BYTES;              // epilogue staging, 1024-aligned
-  static constexpr int STG_WARP_BYTES = 2 * 32 * ROW_BYTES;         // two 32-row x 128-byte buffers per warp
-  static constexpr int BAR_OFF = STG_OFF + EPI_WARPS * STG_WARP_BYTES;
+  static constexpr int STG_SLOT_BYTES = 32 * ROW_BYTES;             // 32 rows x 128 bytes: one warp's block
+  static constexpr int STG_BUF_BYTES = EPI_WARPS * STG_SLOT_BYTES;  // two buffers of four slots [buffer][quarter]: the four
+                                                                    // quarters of a buffer are contiguous (one 16 KiB bulk copy)
+  static constexpr int BAR_OFF = STG_OFF + 2 * STG_BUF_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 5;
   static constexpr int MISC_OFF = BAR_OFF + NUM_BARS * 8;
   static constexpr int TOTAL = MISC_OFF + 32 + 1024;  // + alignment slack
@@ -232,7 +235,8 @@ __host__ __device__ __forceinline__ TileInfo decode_tile(const KParams& p, const
     const int U = s.nt_total;                    // units per row block of one chunk
     const int R = U * (p.ws - 1);                // remote units per row block
     const int rows = s.units_per_chunk / U;      // row blocks (or pairs of them)
-    const int lag = rows < RS_LAG ? rows : RS_LAG;
+    const int want = p.rs_lag > 0 ? p.rs_lag : RS_LAG;
+    const int lag = rows < want ? rows : want;
     const int head = lag * R;
     const int body = (rows - lag) * (R + U);
     int remote_r = -1, own_r = -1;               // index inside the remote / own sequence
@@ -740,8 +744,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
     const int quarter = warp & 3;                   // TMEM lanes this warp may read
     const int row_in_tile = quarter * 32 + lane;
     const bool epi_leader = (warp == 2 && lane == 0);
-    const uint32_t stg_base = smem_base + L::STG_OFF + (warp - 2) * L::STG_WARP_BYTES;
+    const uint32_t stg_all = smem_base + L::STG_OFF;
+    // this warp's slot in staging buffer b
+    auto slot = [&](uint32_t b) { return stg_all + b * (uint32_t)L::STG_BUF_BYTES + (uint32_t)quarter * (uint32_t)L::STG_SLOT_BYTES; };
+    // fp32 sums of an own reduce-scatter block: 32 rows x 256 bytes spread over this warp's two slots
+    // (16-byte unit u of row r: slot u >> 3, byte r * 128 + (u & 7) * 16)
+    auto sum_addr = [&](uint32_t row, uint32_t unit) { return slot(unit >> 3) + row * (uint32_t)ROW_BYTES + ((unit & 7u) << 4); };
     uint32_t stg_count = 0;
+    bool prev_coop = false;   // the previous tile left as cooperative 16 KiB copies issued by the leader
     uint32_t lt = 0;
     const bool tracing = p.trace != nullptr;
     // Reduce-scatter: tiles sent to their owners and not yet announced, oldest first (the same
@@ -753,22 +763,32 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
     bool pq_gen[4] = {false, false, false, false};
     int pq_n = 0;
     auto publish_oldest = [&](int count) {   // count = 1 or 2, count <= pq_n
-      // every store of the four warps for these tiles complete (bulk copies: the issuing lanes'
-      // groups; direct stores: each thread's own, fenced by itself), then the flags
+      // Every store of these tiles complete, then the flags.
+      // Bulk copies are all issued, and their groups tracked, by the leader (warp 2, lane 0). It only waits
+      // for their completion; the system-scope fence and the flag stores are the herald's (warp 3, lane 0),
+      // which the leader meets at a two-warp barrier: a fence.sys waits for whatever its own thread has in
+      // flight, and the leader always has the newest tile's copies on the wire (measured at 8 ranks: 8 us per
+      // fence in the leader). Direct stores (fp32 partials) are each thread's own, fenced by itself, then the
+      // four warps meet and the leader publishes.
       const int newer = pq_newer[count - 1];
       bool generic = pq_gen[0] || (count == 2 && pq_gen[1]);
-      const long long c0 = (tracing && epi_leader) ? clock64() : 0;
-      if (lane == 0) ptx::bulk_wait_group_upto(newer);
-      if (generic) __threadfence_system();
-      ptx::named_bar_sync(2, EPI_WARPS * 32);
-      if (epi_leader) {
+      const bool herald = (warp == 3 && lane == 0);
+      const long long c0 = (tracing && (epi_leader || herald)) ? clock64() : 0;
+      if (generic) {
+        __threadfence_system();
+        ptx::named_bar_sync(2, EPI_WARPS * 32);
+      } else if (warp == 2 || warp == 3) {
+        if (epi_leader) ptx::bulk_wait_group_upto(newer);
+        ptx::named_bar_sync(4, 64);
+      }
+      if (generic ? epi_leader : herald) {
         __threadfence_system();
         ptx::st_relaxed_sys(pq_flag[0], p.epoch);
         if (count == 2) ptx::st_relaxed_sys(pq_flag[1], p.epoch);
-        if (tracing) {
-          unsigned long long* slot = trace_slot(p, lt, TR_PUBLISH);
-          if (slot != nullptr) *slot += (unsigned long long)(clock64() - c0);
-        }
+      }
+      if (tracing && (epi_leader || herald)) {
+        unsigned long long* tslot = trace_slot(p, lt, TR_PUBLISH);
+        if (tslot != nullptr) atomicAdd(tslot, (unsigned long long)(clock64() - c0));
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -808,10 +828,25 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       // Before waiting on the peers, announce what this CTA still owes them: two ranks that each
       // held back their last partial while waiting for the other's would wait forever.
       if (p.mode == MODE_RS && own) publish_pending();
+      // Bulk-copy tiles: all but the newest are announced here, by the leader alone, before it waits for the
+      // next accumulator. Their copies were issued at least a tile's time ago (measured at 8 ranks: a 16 KiB
+      // copy takes about 10 us to be acknowledged when every GPU is sending), so the leader hardly waits,
+      // and the owner learns of a partial one tile after it was sent instead of several.
+      if (p.mode == MODE_RS && p.rs_arena_tma != 0) {
+        while (pq_n > 1) publish_oldest(pq_n > 2 ? 2 : 1);
+      }
       // One thread does the waiting (peers' partials for a tile this rank owns, then the
       // accumulator); its verdict is shared so that all four warps leave the loop together.
+      const bool coop = (p.mode == MODE_RS) && !own && p.rs_arena_tma != 0;   // this tile leaves as cooperative 16 KiB copies
+      if (coop && !prev_coop) {
+        // this warp's own tiled stores must have finished reading its staging slots
+        if (lane == 0) ptx::bulk_wait_group_read<0>();
+        __syncwarp();
+      }
       if (epi_leader) {
         bool good = true;
+        // the other warps are about to reuse slots that the leader's cooperative copies may still be reading
+        if (prev_coop && !coop) ptx::bulk_wait_group_read<0>();
         const long long c0 = tracing ? clock64() : 0;
         if (p.mode == MODE_RS && own && p.ws > 1 && p.rs_arena_tma != 0) {
           // the communication warps acquire the peers' flags and leave the sum of their partials
@@ -873,13 +908,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
 #pragma unroll 1
       for (int g = 0; g < BN / 64; ++g) {
         if (g * 64 >= ti.n_valid) break;   // uniform across the warp
-        const uint32_t stg = stg_base + (stg_count & 1u) * (32 * ROW_BYTES);
+        const uint32_t stg = slot(stg_count & 1u);
         // A tile this rank owns: the peers' bf16 partials of this 32-row x 64-column block are
         // summed first, with coalesced loads (lane i takes 16-byte chunks i, i+32, ... of each
         // 4 KiB block; row-per-thread loads reached a small fraction of the memory rate). The
         // fp32 sums go through both staging buffers (8 KiB) so that each thread can pick up its row.
         const bool own_blocked = (p.mode == MODE_RS) && own && p.ws > 1 && p.rs_arena_tma != 0;
-        if (use_tma || own_blocked) {
+        if ((use_tma && !coop) || own_blocked) {
           // the stores that last used the staging memory must have finished reading it
           if (lane == 0) {
             if (own_blocked) ptx::bulk_wait_group_read<0>(); else ptx::bulk_wait_group_read<1>();
@@ -902,7 +937,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
             const uint32_t Lc = U >> 1, h = U & 1u;
             const uint32_t row = Lc >> 3, sw = row & 7u;
             const uint32_t c = (Lc & 7u) ^ sw;
-            ptx::st_shared_v4(stg_base + row * 256u + (((2u * c + h) ^ sw) << 4), u4[i].x, u4[i].y, u4[i].z, u4[i].w);
+            ptx::st_shared_v4(sum_addr(row, (2u * c + h) ^ sw), u4[i].x, u4[i].y, u4[i].z, u4[i].w);
           }
           __syncwarp();
         }
@@ -961,12 +996,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
             if (own_blocked) {
               // this thread's row of the fp32 sums, half `hf`
               const uint32_t sw = (uint32_t)(lane & 7);
-              const uint32_t base = stg_base + (uint32_t)lane * 256u;
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const uint32_t c = (uint32_t)(hf * 4 + j);
-                const float4 s0 = ptx::ld_shared_f4(base + (((2u * c) ^ sw) << 4));
-                const float4 s1 = ptx::ld_shared_f4(base + (((2u * c + 1u) ^ sw) << 4));
+                const float4 s0 = ptx::ld_shared_f4(sum_addr((uint32_t)lane, (2u * c) ^ sw));
+                const float4 s1 = ptx::ld_shared_f4(sum_addr((uint32_t)lane, (2u * c + 1u) ^ sw));
                 v[8 * j + 0] += s0.x; v[8 * j + 1] += s0.y; v[8 * j + 2] += s0.z; v[8 * j + 3] += s0.w;
                 v[8 * j + 4] += s1.x; v[8 * j + 5] += s1.y; v[8 * j + 6] += s1.z; v[8 * j + 7] += s1.w;
               }
@@ -1011,17 +1045,26 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
             }
           }
           ptx::fence_proxy_async_shared();
-          __syncwarp();
-          if (lane == 0) {
-            if (rs_remote) {
-              // one linear 4 KiB bulk copy of the staging buffer as it is (swizzled) into this
-              // tile's block of the peer's arena; the owner undoes the swizzle when it reads
-              const size_t blk = ((((size_t)p.rank * sched.tiles_per_chunk + ti.tile_in_chunk) * (BN / 64) + g) * 4 + quarter);
-              ptx::bulk_store(p.rs_arena_peer[ti.chunk] + blk * (32 * ROW_BYTES), stg, 32 * ROW_BYTES);
-            } else {
-              ptx::tma_store_2d(tm_st, stg, ti.n0 + g * 64, st_row);
+          if (coop) {
+            // The four warps' 4 KiB blocks of this 64-column group are contiguous both in the staging buffer
+            // and in the owner's arena: ONE linear 16 KiB bulk copy over NVLink, as it is (swizzled; the owner
+            // undoes the swizzle when it reads). Larger copies use the link much better than 4 KiB ones.
+            // Before the four warps meet, the leader makes sure that its earlier copies have finished reading
+            // shared memory, so that after the barrier the other buffer may be overwritten.
+            if (epi_leader) ptx::bulk_wait_group_read<0>();
+            ptx::named_bar_sync(2, EPI_WARPS * 32);
+            if (epi_leader) {
+              const size_t blk = (((size_t)p.rank * sched.tiles_per_chunk + ti.tile_in_chunk) * (BN / 64) + g) * 4;
+              ptx::bulk_store(p.rs_arena_peer[ti.chunk] + blk * (32 * ROW_BYTES), stg_all + (stg_count & 1u) * (uint32_t)L::STG_BUF_BYTES,
+                              EPI_WARPS * 32 * ROW_BYTES);
+              ptx::bulk_commit_group();
             }
-            ptx::bulk_commit_group();
+          } else {
+            __syncwarp();
+            if (lane == 0) {
+              ptx::tma_store_2d(tm_st, stg, ti.n0 + g * 64, st_row);
+              ptx::bulk_commit_group();
+            }
           }
           note_commit();
           ++stg_count;
@@ -1035,6 +1078,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       }
       if (tracing && epi_leader) trace_put(p, lt, TR_EPI_END_T, globaltimer_ns());
 
+      prev_coop = coop;
       if (p.mode == MODE_RS && own) ++own_seen;
       if (rs_remote) {
         // The owner's flag for this tile is released (two tiles at a time) once the queue of four is full,
@@ -1076,42 +1120,44 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
         ptx::named_bar_sync(3, COMM_WARPS * 32);
         if (sum_verdict[done & 1u] == 0u) break;
         const int groups = (ti.n_valid + 63) / 64;
-        for (int blk16 = cw; blk16 < groups * 4; blk16 += COMM_WARPS) {
+        // Unit of work: half of a 4 KiB block (16 rows x 64 columns), with ALL peers' copies of it loaded
+        // before the first add: one memory round trip per unit (the partials come from HBM, they arrived
+        // over NVLink), where loading two peers at a time took four.
+        for (int unit = cw; unit < groups * 8; unit += COMM_WARPS) {
+          const int blk16 = unit >> 1, half = unit & 1;
           const size_t blk = ((size_t)ti.tile_in_chunk * (BN / 64) * 4 + blk16);
-          const uint8_t* base = p.rs_arena_local + blk * (32 * ROW_BYTES);
-          float sum[64];
+          const uint8_t* base = p.rs_arena_local + blk * (32 * ROW_BYTES) + half * (16 * ROW_BYTES);
+          uint4 q[MAX_WORLD - 1][4];
 #pragma unroll
-          for (int j = 0; j < 64; ++j) sum[j] = 0.0f;
-          for (int s0 = 1; s0 < p.ws; s0 += 2) {
-            uint4 q[2][8];
+          for (int u = 0; u < MAX_WORLD - 1; ++u) {
+            if (u < p.ws - 1) {
+              const uint8_t* bp = base + (size_t)((p.rank + 1 + u) % p.ws) * src_stride;
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              if (s0 + u < p.ws) {
-                const uint8_t* bp = base + (size_t)((p.rank + s0 + u) % p.ws) * src_stride;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) q[u][i] = ptx::ld_cg_v4(bp + (size_t)(i * 32 + lane) * 16);
-              }
+              for (int i = 0; i < 4; ++i) q[u][i] = ptx::ld_cg_v4(bp + (size_t)(i * 32 + lane) * 16);
             }
+          }
+          float sum[32];
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              if (s0 + u < p.ws) {
+          for (int j = 0; j < 32; ++j) sum[j] = 0.0f;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  const uint32_t w[4] = {q[u][i].x, q[u][i].y, q[u][i].z, q[u][i].w};
+          for (int u = 0; u < MAX_WORLD - 1; ++u) {
+            if (u < p.ws - 1) {
 #pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    sum[8 * i + 2 * e] += __uint_as_float(w[e] << 16);
-                    sum[8 * i + 2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
-                  }
+              for (int i = 0; i < 4; ++i) {
+                const uint32_t w[4] = {q[u][i].x, q[u][i].y, q[u][i].z, q[u][i].w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  sum[8 * i + 2 * e] += __uint_as_float(w[e] << 16);
+                  sum[8 * i + 2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
                 }
               }
             }
           }
-          // chunk L = i*32+lane of the bf16 block becomes units 2L and 2L+1 of the 8 KiB fp32 block
+          // chunk L = half*128 + i*32 + lane of the bf16 block becomes units 2L and 2L+1 of the 8 KiB fp32 block
           float4* op = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(p.rs_sum_local) + blk * (size_t)(64 * ROW_BYTES));
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int Lc = i * 32 + lane;
+          for (int i = 0; i < 4; ++i) {
+            const int Lc = half * 128 + i * 32 + lane;
             op[2 * Lc] = make_float4(sum[8 * i], sum[8 * i + 1], sum[8 * i + 2], sum[8 * i + 3]);
             op[2 * Lc + 1] = make_float4(sum[8 * i + 4], sum[8 * i + 5], sum[8 * i + 6], sum[8 * i + 7]);
           }

@@ -89,21 +89,14 @@ template <int N>
 __device__ __forceinline__ void bulk_wait_group() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
-// Same with a run-time bound (0..12); larger values wait for everything.
+// Same with a run-time bound (0..20); larger values wait for everything.
 __device__ __forceinline__ void bulk_wait_group_upto(int n) {
   switch (n) {
-    case 9: bulk_wait_group<9>(); break;
-    case 10: bulk_wait_group<10>(); break;
-    case 11: bulk_wait_group<11>(); break;
-    case 12: bulk_wait_group<12>(); break;
-    case 1: bulk_wait_group<1>(); break;
-    case 2: bulk_wait_group<2>(); break;
-    case 3: bulk_wait_group<3>(); break;
-    case 4: bulk_wait_group<4>(); break;
-    case 5: bulk_wait_group<5>(); break;
-    case 6: bulk_wait_group<6>(); break;
-    case 7: bulk_wait_group<7>(); break;
-    case 8: bulk_wait_group<8>(); break;
+#define APK_WG_CASE(N) case N: bulk_wait_group<N>(); break;
+    APK_WG_CASE(1) APK_WG_CASE(2) APK_WG_CASE(3) APK_WG_CASE(4) APK_WG_CASE(5) APK_WG_CASE(6) APK_WG_CASE(7)
+    APK_WG_CASE(8) APK_WG_CASE(9) APK_WG_CASE(10) APK_WG_CASE(11) APK_WG_CASE(12) APK_WG_CASE(13) APK_WG_CASE(14)
+    APK_WG_CASE(15) APK_WG_CASE(16) APK_WG_CASE(17) APK_WG_CASE(18) APK_WG_CASE(19) APK_WG_CASE(20)
+#undef APK_WG_CASE
     default: bulk_wait_group<0>(); break;
   }
 }
