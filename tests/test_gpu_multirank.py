@@ -16,7 +16,7 @@ def _ngpus():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
-def _worker(rank, world, golden):
+def _worker(rank, world, golden, golden_fp8):
     import torch.distributed as dist
 
     import autoparallel_b200.asynctp_ops  # noqa: F401
@@ -26,6 +26,15 @@ def _worker(rank, world, golden):
     dev = torch.device("cuda", rank)
     g = dist.group.WORLD.group_name
     ns = torch.ops._ap_symm_mem
+
+    def err(out, ref64_fn):
+        """Relative Frobenius error against an fp64 reference computed on the device (the large cases would
+        take minutes on the host cores)."""
+        ref = ref64_fn()
+        return ((out.double() - ref).norm() / ref.norm().clamp_min(1e-300)).item()
+
+    def d64(t):
+        return t.to(dev).double()
 
     # ---- golden fixtures (world 2 only): the reference's own outputs for these inputs
     if world == 2:
@@ -42,6 +51,49 @@ def _worker(rank, world, golden):
                 out = ns.fused_matmul_reduce_scatter(rec["A"].to(dev), rec["B"].to(dev), rec["op"], rec["scatter_dim"], g)
                 assert out.shape == rec["out"].shape
                 torch.testing.assert_close(out.cpu().float(), rec["out"].float(), rtol=2 ** -6, atol=4e-3)
+        # ---- the reference's fp8 outputs (tests/golden/asynctp_golden_fp8.pt and the tensor-wise cases of the first
+        #      fixture) through the CUDA path: every scale mode of the all-gather, bias, result scale, 3-D operands,
+        #      both output types, reduce-scatter along dim 0 and 1. Same calls and tolerances as the CPU run of the
+        #      host path (tests/test_host_end_to_end_cpu.py).
+        dts = {"torch.bfloat16": torch.bfloat16, "torch.float32": torch.float32}
+
+        def close(o, gold, rs=False):
+            assert o.shape == gold.shape and o.dtype == gold.dtype, (o.shape, gold.shape, o.dtype, gold.dtype)
+            if rs:   # the reference rounds every partial to bf16 before the sum, this path keeps its own in fp32
+                torch.testing.assert_close(o.cpu().float(), gold.float(), rtol=2 ** -6, atol=max(4e-3, 2 ** -7 * float(gold.float().abs().max())))
+            elif o.dtype == torch.float32:
+                torch.testing.assert_close(o.cpu(), gold, rtol=1e-5, atol=1e-5)
+            else:
+                torch.testing.assert_close(o.cpu().float(), gold.float(), rtol=2 ** -7, atol=2e-3)
+
+        n_fp8 = 0
+        for rec in mine:
+            if rec["kind"] == "smm_rs":
+                out = ns.fused_scaled_matmul_reduce_scatter(
+                    rec["A"].to(dev), rec["B_t"].to(dev).t(), rec["A_scale"].to(dev), rec["B_scale"].to(dev), rec["op"], 0, 0, g,
+                    [rec["shape"][0], rec["N"]], None, None, torch.bfloat16, False)
+                close(out, rec["out"], rs=True)
+                n_fp8 += 1
+        for rec in golden_fp8["ranks"][rank]:
+            opt = lambda t: None if t is None else t.to(dev)   # noqa: E731
+            if rec["kind"] == "sag_mm":
+                Bs = [bt.to(dev).t() for bt in rec["Bs_t"]]
+                A_out, outs = ns.fused_all_gather_scaled_matmul(
+                    rec["A_shard"].to(dev), Bs, rec["A_scale"].to(dev), [s.to(dev) for s in rec["B_scales"]], rec["gather_dim"], g,
+                    [opt(b) for b in rec["biases"]], [opt(r) for r in rec["result_scales"]], [dts[d] for d in rec["out_dtypes"]],
+                    [False] * len(Bs))
+                what = (rec["mode"], rec["shape"], rec["gather_dim"])
+                assert A_out.shape == rec["A_out"].shape, what
+                assert torch.equal(A_out.contiguous().cpu().view(torch.uint8), rec["A_out"].view(torch.uint8)), what
+                for o, gold in zip(outs, rec["outs"]):
+                    close(o, gold)
+            else:
+                out = ns.fused_scaled_matmul_reduce_scatter(
+                    rec["A"].to(dev), rec["B_t"].to(dev).t(), rec["A_scale"].to(dev), rec["B_scale"].to(dev), rec["op"],
+                    rec["scatter_dim"], rec["scatter_dim"], g, list(rec["output_shape"]), None, None, torch.bfloat16, False)
+                close(out, rec["out"], rs=True)
+            n_fp8 += 1
+        assert n_fp8 == 2 + 12, n_fp8
 
     # ---- all-gather -> matmul against the oracle, ragged and multi-B shapes, both B layouts
     for rows, K, Ns, return_A, transposed in [
@@ -58,24 +110,29 @@ def _worker(rank, world, golden):
         A_ref, outs_ref = orc.all_gather_matmul_local(shards, Bs, 0, return_A)
         if return_A:
             assert torch.equal(A_out.cpu(), A_ref)
+        A64 = d64(torch.cat(shards))
         for o, b in zip(outs, Bs):
-            err = orc.rel_fro_error(o, torch.cat(shards).double() @ b.double())
-            assert err <= BF16_TOL, (rows, K, Ns, err)
+            e = err(o, lambda: A64 @ d64(b))
+            assert e <= BF16_TOL, (rows, K, Ns, e)
+        del A64
 
     # ---- matmul -> reduce-scatter against the oracle
     for M, K, N, op in [(512, 256, 256, "sum"), (2000 // world * world, 520, 264, "avg"), (8192, 1792, 4096, "sum"), (128 * world, 64, 8, "sum")]:
         As = [orc.activations(20 + r, M, K) for r in range(world)]
         Ws = [orc.weights(30 + r, K, N) for r in range(world)]
         out = ns.fused_matmul_reduce_scatter(As[rank].to(dev), Ws[rank].to(dev), op, 0, g)
-        ref64 = sum(a.double() @ w.double() for a, w in zip(As, Ws))
+        lo, hi = rank * (M // world), (rank + 1) * (M // world)
+        ref64 = sum(d64(a[lo:hi]) @ d64(w) for a, w in zip(As, Ws))
         if op == "avg":
             ref64 = ref64 / world
-        ref64 = ref64.chunk(world)[rank]
         assert out.shape == ref64.shape
-        err = orc.rel_fro_error(out, ref64)
-        assert err <= BF16_TOL, (M, K, N, op, err)
-        oracle_out = orc.matmul_reduce_scatter_local(As, Ws, op, 0)[rank]
-        assert err <= 1.5 * orc.rel_fro_error(oracle_out, ref64) + 1e-4
+        e = err(out, lambda: ref64)
+        assert e <= BF16_TOL, (M, K, N, op, e)
+        # never further from fp64 than the reference's decomposition (bf16 partials summed, autoparallel/asynctp_ops.py:1180-1185)
+        parts = torch.stack([(a[lo:hi].to(dev) @ w.to(dev)).float() for a, w in zip(As, Ws)])
+        oracle_out = (parts.sum(0) if op == "sum" else parts.mean(0)).bfloat16()
+        assert e <= 1.5 * err(oracle_out, lambda: ref64) + 1e-4
+        del ref64, parts
 
     # ---- 3-D operands, gather / scatter along dim 1
     sh3 = [orc.activations(40 + r, 4 * 32, 64).view(4, 32, 64) for r in range(world)]
@@ -162,10 +219,10 @@ def _worker(rank, world, golden):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_fused_ops_multirank(world, golden):
+def test_fused_ops_multirank(world, golden, golden_fp8):
     if _ngpus() < world:
         pytest.skip(f"needs {world} GPUs")
     from autoparallel_b200.build import build_native
 
     build_native()
-    run_ranks(_worker, world, golden, backend="nccl")
+    run_ranks(_worker, world, golden, golden_fp8, backend="nccl")

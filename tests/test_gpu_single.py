@@ -404,6 +404,116 @@ def test_full_size_llama70b_fp8_properties(group):
     assert ((lhs - rhs).norm() / rhs.norm()).item() <= FP8_TOL
 
 
+def test_full_size_llama8b_attention_properties(group):
+    """BASELINE config 3 on one rank: 32768 tokens x 4096, wq/wk/wv [4096, 512 / 128 / 128], wo [512, 4096]
+    (mixed output widths in one launch, and a reduce-scatter matmul with only eight k-blocks per tile)."""
+    torch.manual_seed(2)
+    A = torch.randn(32768, 4096, device="cuda").bfloat16()
+    ws = [(torch.randn(4096, n, device="cuda") * 0.02).bfloat16() for n in (512, 128, 128)]
+    _, outs = torch.ops._ap_symm_mem.fused_all_gather_matmul(A, ws, 0, group, return_A=False)
+    for o, w in zip(outs, ws):
+        assert o.shape == (32768, w.shape[1])
+        _freivalds(o, A, w, BF16_TOL)
+    x = torch.randn(32768, 512, device="cuda").bfloat16()
+    wo = (torch.randn(512, 4096, device="cuda") * 0.02).bfloat16()
+    out = torch.ops._ap_symm_mem.fused_matmul_reduce_scatter(x, wo, "sum", 0, group)
+    assert out.shape == (32768, 4096)
+    _freivalds(out, x, wo, BF16_TOL)
+    avg = torch.ops._ap_symm_mem.fused_matmul_reduce_scatter(x, wo, "avg", 0, group)
+    assert torch.equal(avg, out)          # a group of one: the mean of one partial is that partial
+
+
+def test_full_size_llama70b_fp8_reduce_scatter_properties(group):
+    """The reduce-scatter side of BASELINE config 4 on one rank: [16384, 3584] e4m3 row-wise x w2 [3584, 8192]
+    column-wise -> bf16."""
+    orc = _orc()
+    torch.manual_seed(3)
+    x = torch.randn(16384, 3584, device="cuda")
+    w = torch.randn(3584, 8192, device="cuda") * 0.02
+    sa = x.abs().amax(1, keepdim=True) / 448
+    sb = w.abs().amax(0, keepdim=True) / 448
+    a8 = (x / sa).to(orc.FP8)
+    b8 = (w / sb).to(orc.FP8).t().contiguous().t()
+    out = torch.ops._ap_symm_mem.fused_scaled_matmul_reduce_scatter(
+        a8, b8, sa, sb, "sum", 0, 0, group, [16384, 8192], None, None, torch.bfloat16, False
+    )
+    assert out.shape == (16384, 8192) and out.dtype == torch.bfloat16
+    g = torch.Generator(device="cuda").manual_seed(5)
+    v = torch.randn(8192, 4, device="cuda", dtype=torch.float64, generator=g)
+    lhs = out.double() @ v
+    rhs = (a8.double() * sa.double()) @ ((b8.double() * sb.double()) @ v)
+    assert ((lhs - rhs).norm() / rhs.norm()).item() <= FP8_TOL
+    # against the library's own row-wise _scaled_mm on the same operands: both round an fp32 result to bf16
+    lib = torch._scaled_mm(a8, b8, sa, sb, out_dtype=torch.bfloat16)
+    assert ((out.double() - lib.double()).norm() / lib.double().norm()).item() <= 2 ** -8
+
+
+def test_scaled_reduce_scatter_with_a_folded_scatter_dim(group):
+    """A scatter dim that a pre-matmul reshape folded into the rows (orig_scatter_dim 1, 0 after the reshape,
+    output_shape [B, S, N] with B > 1; autoparallel/asynctp.py:896-940 emits it). The reference's CUDA body
+    returns row chunk `rank` of the flattened [B*S, N] product viewed as [B, S/world, N]
+    (autoparallel/asynctp_ops.py:1375-1423); this is that layout, here on a group of one."""
+    orc = _orc()
+    Bt, S, K, N = 3, 64, 256, 136
+    a8, sa, b8, sb = _fp8_case(orc, Bt * S, K, N, seed=9)
+    out = torch.ops._ap_symm_mem.fused_scaled_matmul_reduce_scatter(
+        a8.cuda(), b8.cuda().t().contiguous().t(), sa.cuda(), sb.cuda(), "sum", 1, 0, group, [Bt, S, N], None, None,
+        torch.bfloat16, False,
+    )
+    assert out.shape == (Bt, S, N)
+    ref64 = ((a8.double() * sa.double()) @ (b8.double() * sb.double())).view(Bt, S, N)     # rows in (b, s) order
+    assert orc.rel_fro_error(out, ref64) <= FP8_TOL
+    # row r of the flattened product lands at [r // S, r % S]: a probe that differs per row
+    row_norm = out.float().flatten(0, 1).norm(dim=1).cpu()
+    assert torch.allclose(row_norm, ref64.flatten(0, 1).norm(dim=1).float(), rtol=2e-2)
+
+
+def test_more_than_four_operands(group):
+    """Six Bs share one gathered A: one fused launch for four, one local launch for the rest."""
+    from autoparallel_b200 import _native as nat
+
+    orc = _orc()
+    A = orc.activations(0, 300, 264)
+    Bs = [orc.weights(20 + i, 264, 8 * (i + 3)) for i in range(6)]
+    before = nat.lib().apk_launch_count()
+    A_out, outs = _ag(A, Bs, 0, group)
+    assert nat.lib().apk_launch_count() == before + 2
+    assert torch.equal(A_out.cpu(), A)
+    for o, b in zip(outs, Bs):
+        assert orc.rel_fro_error(o, A.double() @ b.double()) <= BF16_TOL
+
+
+def test_timeline_stamps_are_ordered(group):
+    """apk_set_trace: every tile of a launch leaves one record, and inside a record the stamps follow the
+    pipeline: first load <= first MMA <= last MMA committed <= accumulator complete <= epilogue done, all
+    inside the CTA's own begin / end."""
+    from autoparallel_b200 import timeline
+
+    A = torch.randn(4096, 1024, device="cuda").bfloat16()
+    B = (torch.randn(1024, 512, device="cuda") * 0.02).bfloat16()
+    dev = torch.device("cuda", 0)
+    with timeline.capture(dev) as tl:
+        torch.ops._ap_symm_mem.fused_all_gather_matmul(A, [B], 0, group, return_A=False)
+        rec = tl.records()
+    F = timeline.F
+    used = rec[rec[:, F["tile"]] > 0]
+    tiles = (4096 // 128) * (512 // 256)
+    assert used.shape[0] == tiles and sorted((used[:, F["tile"]] - 1).tolist()) == sorted(list(range(tiles // 2)) * 2)   # pairs: both CTAs record
+    mma = used[used[:, F["mma_t"]] > 0]          # the CTA of a pair that issues the MMAs
+    assert mma.shape[0] == tiles // 2
+    assert bool((mma[:, F["load_t"]] <= mma[:, F["mma_t"]]).all())
+    assert bool((mma[:, F["mma_t"]] <= mma[:, F["commit_t"]]).all())
+    assert bool((mma[:, F["commit_t"]] <= mma[:, F["tfull_t"]] + 1000).all())   # globaltimer ticks are coarse (up to 1 us)
+    assert bool((used[:, F["tfull_t"]] <= used[:, F["epi_end_t"]]).all())
+    s = timeline.summary(rec)
+    assert s["tiles"] == tiles and 0 < s["span_us"] < 1e4 and 500 < s["sm_mhz_in_kernel"] < 2500
+    # off again: a launch after the capture leaves the (zeroed) buffer alone
+    tl.clear()
+    torch.ops._ap_symm_mem.fused_all_gather_matmul(A, [B], 0, group, return_A=False)
+    torch.cuda.synchronize()
+    assert int(tl.buf.abs().sum()) == 0
+
+
 # --------------------------------------------------------------------------------------- C ABI, status word
 def test_c_abi_direct_call_and_alignment_error(group):
     from autoparallel_b200 import _native as nat
