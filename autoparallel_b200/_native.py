@@ -22,6 +22,7 @@ APK_ERR_TIMEOUT = -4
 APK_BF16 = 0
 APK_E4M3 = 1
 APK_F32 = 2
+APK_F16 = 3
 
 APK_SCALE_NONE = 0
 APK_SCALE_SCALAR = 1

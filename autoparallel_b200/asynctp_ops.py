@@ -244,20 +244,21 @@ def _flat_row_scale(A: torch.Tensor, A_scale: torch.Tensor) -> torch.Tensor:
 
 
 # =============================================================================== native path
-_DTYPE_CODE = {torch.bfloat16: nat.APK_BF16, torch.float8_e4m3fn: nat.APK_E4M3, torch.float32: nat.APK_F32}
+_DTYPE_CODE = {torch.bfloat16: nat.APK_BF16, torch.float8_e4m3fn: nat.APK_E4M3, torch.float32: nat.APK_F32, torch.float16: nat.APK_F16}
 
 
 def _in_dtype_code(t: torch.Tensor, what: str) -> int:
-    if t.dtype not in (torch.bfloat16, torch.float8_e4m3fn):
+    if t.dtype not in (torch.bfloat16, torch.float16, torch.float8_e4m3fn):
         raise NotImplementedError(
-            f"{what}: the sm_100a kernels take bfloat16 or float8_e4m3fn operands, got {t.dtype}"
+            f"{what}: the sm_100a kernels take bfloat16, float16 or float8_e4m3fn operands, got {t.dtype} "
+            "(the tensor cores have no fp32 input format; cast the operands)"
         )
     return _DTYPE_CODE[t.dtype]
 
 
 def _out_dtype_code(dt: torch.dtype, what: str) -> int:
-    if dt not in (torch.bfloat16, torch.float32):
-        raise NotImplementedError(f"{what}: output dtype must be bfloat16 or float32, got {dt}")
+    if dt not in (torch.bfloat16, torch.float16, torch.float32):
+        raise NotImplementedError(f"{what}: output dtype must be bfloat16, float16 or float32, got {dt}")
     return _DTYPE_CODE[dt]
 
 
@@ -486,8 +487,8 @@ def _ag_gemm_last_dim_native(
         raise ValueError("at least one B operand is needed")
     group = c10d._resolve_process_group(group_name)
     world = group.size()
-    if A_shard.dtype != torch.bfloat16:
-        raise NotImplementedError(f"all-gather matmul along the last dim takes bfloat16 operands, got {A_shard.dtype}")
+    if A_shard.dtype not in (torch.bfloat16, torch.float16):
+        raise NotImplementedError(f"all-gather matmul along the last dim takes bfloat16 or float16 operands, got {A_shard.dtype}")
     lead = list(A_shard.shape[:-1])
     A2 = _aligned(A_shard.flatten(0, -2).contiguous())
     rows, Kc = A2.shape
@@ -508,7 +509,7 @@ def _ag_gemm_last_dim_native(
     wsp = symm.get_workspace(group_name, A2.device)
     args = nat.ApkAgGemmArgs()
     keep: list = [A2]
-    args.dtype = nat.APK_BF16
+    args.dtype = _DTYPE_CODE[A_shard.dtype]
     args.rows_per_rank = rows
     args.K = Kc
     args.nB = len(Bs)
@@ -562,9 +563,12 @@ def _gemm_rs_native(
         raise ValueError(f"the scatter dimension ({M} rows after flattening) is not divisible by the group size {world}")
     A2 = _aligned(A2.contiguous())
     out_shape = (M, B.shape[1] // world) if scatter_cols else (M // world, B.shape[1])
-    out = A2.new_empty(out_shape, dtype=out_dtype)
+    # Partials cross NVLink as bf16 or fp32. For a float16 result with peers they travel as fp32 (closer to
+    # fp64 than the reference's float16 partials, at twice the bytes) and the sum is rounded once at the end.
+    via_f32 = out_dtype == torch.float16 and world > 1
+    out = A2.new_empty(out_shape, dtype=torch.float32 if via_f32 else out_dtype)
     if M == 0:
-        return out   # no rows: no collective takes place and the group's epoch does not move
+        return out.to(out_dtype)   # no rows: no collective takes place and the group's epoch does not move
     wsp = symm.get_workspace(group_name, A2.device)
     args = nat.ApkGemmRsArgs()
     keep: list = [A2]
@@ -585,7 +589,7 @@ def _gemm_rs_native(
     wsp.ensure(L.apk_gemm_rs_arena_bytes(C.byref(args), world), 256)
     comm = wsp.next_comm()
     nat.check(L.apk_gemm_rs(C.byref(comm), C.byref(args), _stream_ptr(A2.device)))
-    return out
+    return out.to(torch.float16) if via_f32 else out
 
 
 def _check_reduce_op(reduce_op: str) -> None:

@@ -69,7 +69,7 @@ int encode_2d(CUtensorMap* tm, int dtype, const void* base, uint64_t cols, uint6
   EncodeFn enc;
   int rc = get_encode(&enc);
   if (rc != APK_OK) return rc;
-  const uint64_t es = (dtype == APK_BF16) ? 2 : 1;
+  const uint64_t es = (dtype == APK_E4M3) ? 1 : 2;
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return fail(APK_ERR_ARG, "%s: base pointer must be 16-byte aligned", what);
   if ((ld * es) % 16 != 0) return fail(APK_ERR_ARG, "%s: row pitch (%llu bytes) must be a multiple of 16", what, (unsigned long long)(ld * es));
   if (box_cols * es != apk::ROW_BYTES) return fail(APK_ERR_ARG, "%s: inner box must span 128 bytes", what);
@@ -78,7 +78,9 @@ int encode_2d(CUtensorMap* tm, int dtype, const void* base, uint64_t cols, uint6
   cuuint64_t strides[1] = {ld * es};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(tm, dtype == APK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+  const CUtensorMapDataType tmt = dtype == APK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                  : dtype == APK_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = enc(tm, tmt, 2,
                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(APK_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed with %d", what, (int)r);
@@ -285,13 +287,14 @@ int fill_operand(apk::KParams* kp, int b, const apk_operand& op_in, int dtype, i
   const uint64_t b_cols = b_cols_total > 0 ? (uint64_t)b_cols_total : (uint64_t)op.N;
   if (op.B == nullptr || op.out == nullptr) return fail(APK_ERR_ARG, "%s: null B or out", what);
   if (op.N <= 0) return fail(APK_ERR_ARG, "%s: N must be positive", what);
-  if (op.out_dtype != APK_BF16 && op.out_dtype != APK_F32) return fail(APK_ERR_ARG, "%s: out dtype must be bf16 or f32", what);
+  if (op.out_dtype != APK_BF16 && op.out_dtype != APK_F32 && op.out_dtype != APK_F16)
+    return fail(APK_ERR_ARG, "%s: out dtype must be bf16, f16 or f32", what);
   const int oes = op.out_dtype == APK_F32 ? 4 : 2;
   const int vec = 16 / oes;
   if (op.N % vec != 0) return fail(APK_ERR_ARG, "%s: N (%d) must be a multiple of %d", what, op.N, vec);
   if ((reinterpret_cast<uintptr_t>(op.out) & 15u) != 0 || (op.ldo * oes) % 16 != 0)
     return fail(APK_ERR_ARG, "%s: output must be 16-byte aligned with a 16-byte multiple pitch", what);
-  const int bke = dtype == APK_BF16 ? 64 : 128;
+  const int bke = dtype == APK_E4M3 ? 128 : 64;
   int rc;
   if (op.n_major) {
     rc = encode_2d(&kp->tmB[b], dtype, op.B, b_cols, (uint64_t)K, (uint64_t)op.ldb, bke, bke, what);
@@ -306,9 +309,10 @@ int fill_operand(apk::KParams* kp, int b, const apk_operand& op_in, int dtype, i
   kp->out[b] = op.out;
   kp->ldo[b] = op.ldo;
   kp->out_fp32[b] = op.out_dtype == APK_F32;
-  if (op.out_dtype == APK_BF16) {
+  kp->out_f16[b] = op.out_dtype == APK_F16;
+  if (op.out_dtype != APK_F32) {
     // stores: 32 rows x 64 columns per TMA instruction, clipped at N by the descriptor
-    rc = encode_2d(&kp->tmOut[b], APK_BF16, op.out, (uint64_t)op.N, (uint64_t)out_rows, (uint64_t)op.ldo, 64, 32, what);
+    rc = encode_2d(&kp->tmOut[b], op.out_dtype, op.out, (uint64_t)op.N, (uint64_t)out_rows, (uint64_t)op.ldo, 64, 32, what);
     if (rc != APK_OK) return rc;
     kp->out_tma[b] = 1;
   }
@@ -428,7 +432,7 @@ int apk_symm_unimport(void* ptr) {
 
 uint64_t apk_ag_gemm_arena_bytes(const apk_ag_gemm_args* a, int32_t world) {
   if (a == nullptr || world <= 1) return 0;
-  const uint64_t es = a->dtype == APK_BF16 ? 2 : 1;
+  const uint64_t es = a->dtype == APK_E4M3 ? 1 : 2;
   uint64_t bytes = align_up((uint64_t)a->rows_per_rank * (uint64_t)a->K * es, 256);
   if (a->a_scale_mode == APK_SCALE_VECTOR) bytes += align_up((uint64_t)a->rows_per_rank * 4, 256);
   return bytes;
@@ -460,13 +464,13 @@ int apk_ag_gemm(const apk_comm* comm, const apk_ag_gemm_args* a, void* stream_) 
   int rc = check_comm(comm);
   if (rc != APK_OK) return rc;
   if (a == nullptr) return fail(APK_ERR_ARG, "args is null");
-  if (a->dtype != APK_BF16 && a->dtype != APK_E4M3) return fail(APK_ERR_ARG, "dtype must be bf16 or e4m3");
+  if (a->dtype != APK_BF16 && a->dtype != APK_E4M3 && a->dtype != APK_F16) return fail(APK_ERR_ARG, "dtype must be bf16, f16 or e4m3");
   if (a->nB < 1 || a->nB > APK_MAX_B) return fail(APK_ERR_ARG, "nB must be in [1, %d]", APK_MAX_B);
   if (a->rows_per_rank < 0 || a->K <= 0) return fail(APK_ERR_ARG, "bad shape");
   if (a->rows_per_rank == 0) return APK_OK;
   if (a->A_shard == nullptr) return fail(APK_ERR_ARG, "A_shard is null");
   const int ws = comm->world;
-  const int es = a->dtype == APK_BF16 ? 2 : 1;
+  const int es = a->dtype == APK_E4M3 ? 1 : 2;
   const int64_t M = (int64_t)a->rows_per_rank * ws;
   if (M > 0x7fffffffLL) return fail(APK_ERR_ARG, "M too large");
   const bool need_gathered = ws > 1 || a->return_A;
@@ -485,18 +489,19 @@ int apk_ag_gemm(const apk_comm* comm, const apk_ag_gemm_args* a, void* stream_) 
   kp.M = (int32_t)M;
   kp.K = a->K;
   kp.ag_ksplit = a->gather_k ? 1 : 0;
-  if (a->gather_k && (a->dtype != APK_BF16 || a->a_scale_mode != APK_SCALE_NONE))
-    return fail(APK_ERR_ARG, "gather_k supports bf16 without scales only");
+  if (a->gather_k && (a->dtype == APK_E4M3 || a->a_scale_mode != APK_SCALE_NONE))
+    return fail(APK_ERR_ARG, "gather_k supports bf16 / f16 without scales only");
   if (a->gather_k && (int64_t)a->K * ws > 0x7fffffffLL) return fail(APK_ERR_ARG, "K too large");
   // K-split: a k-block that runs past a shard's K would multiply A's zero fill with the NEXT rank's rows of B
   // (0 * Inf = NaN where the reference's cat(A) @ B has none), so every slice must be whole k-blocks.
   if (a->gather_k && ws > 1 && a->K % 64 != 0) return fail(APK_ERR_ARG, "gather_k needs K (%d) to be a multiple of 64", a->K);
   kp.rows_per_rank = a->rows_per_rank;
   kp.elem_bytes = es;
+  kp.in_f16 = a->dtype == APK_F16;
   int max_n = 0;
   for (int b = 0; b < a->nB; ++b) max_n = a->Bs[b].N > max_n ? a->Bs[b].N : max_n;
   const int bn = max_n <= 128 ? 128 : 256;
-  const int bke = a->dtype == APK_BF16 ? 64 : 128;
+  const int bke = a->dtype == APK_E4M3 ? 128 : 64;
   rc = encode_2d(&kp.tmA0, a->dtype, a->A_shard, (uint64_t)a->K, (uint64_t)a->rows_per_rank, (uint64_t)a->lda, bke, apk::BM, "A_shard");
   if (rc != APK_OK) return rc;
   if (need_gathered) {
@@ -568,7 +573,7 @@ int apk_gemm_rs(const apk_comm* comm, const apk_gemm_rs_args* a, void* stream_) 
   int rc = check_comm(comm);
   if (rc != APK_OK) return rc;
   if (a == nullptr) return fail(APK_ERR_ARG, "args is null");
-  if (a->dtype != APK_BF16 && a->dtype != APK_E4M3) return fail(APK_ERR_ARG, "dtype must be bf16 or e4m3");
+  if (a->dtype != APK_BF16 && a->dtype != APK_E4M3 && a->dtype != APK_F16) return fail(APK_ERR_ARG, "dtype must be bf16, f16 or e4m3");
   const int ws = comm->world;
   if (a->M < 0 || a->K <= 0) return fail(APK_ERR_ARG, "bad shape");
   if (!a->scatter_cols && a->M % ws != 0) return fail(APK_ERR_ARG, "M (%d) must be divisible by the group size (%d)", a->M, ws);
@@ -577,7 +582,7 @@ int apk_gemm_rs(const apk_comm* comm, const apk_gemm_rs_args* a, void* stream_) 
   if (a->M == 0) return APK_OK;
   if (a->A == nullptr) return fail(APK_ERR_ARG, "A is null");
   if (a->reduce_op != APK_REDUCE_SUM && a->reduce_op != APK_REDUCE_AVG) return fail(APK_ERR_ARG, "reduce_op must be sum or avg");
-  const int es = a->dtype == APK_BF16 ? 2 : 1;
+  const int es = a->dtype == APK_E4M3 ? 1 : 2;
   if (((int64_t)a->K * es) % 16 != 0) return fail(APK_ERR_ARG, "K * element size must be a multiple of 16 bytes");
   DeviceInfo di;
   rc = device_info(&di);
@@ -596,8 +601,11 @@ int apk_gemm_rs(const apk_comm* comm, const apk_gemm_rs_args* a, void* stream_) 
   const int width = a->scatter_cols ? a->B.N / ws : a->B.N;   // columns of one destination's part
   kp.rs_slot_rows = (int32_t)align_up((uint64_t)kp.rows_per_rank, apk::BM);
   kp.elem_bytes = es;
+  kp.in_f16 = a->dtype == APK_F16;
+  if (ws > 1 && a->B.out_dtype == APK_F16)
+    return fail(APK_ERR_ARG, "reduce-scatter partials travel as bf16 or f32: with peers, ask for an f32 output and round it to f16 afterwards");
   const int bn = width <= 128 ? 128 : 256;
-  const int bke = a->dtype == APK_BF16 ? 64 : 128;
+  const int bke = a->dtype == APK_E4M3 ? 128 : 64;
   rc = encode_2d(&kp.tmA0, a->dtype, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda, bke, apk::BM, "A");
   if (rc != APK_OK) return rc;
   {
@@ -824,7 +832,7 @@ extern "C" int apk_ag_gemm_static(const apk_comm* comm, const apk_ag_gemm_args* 
   if (a == nullptr) return fail(APK_ERR_ARG, "args is null");
   if (a->rows_per_rank < 0 || a->K <= 0 || comm->world < 1 || comm->world > APK_MAX_WORLD)
     return fail(APK_ERR_ARG, "bad shape or group size");
-  const uint64_t es = a->dtype == APK_BF16 ? 2 : 1;
+  const uint64_t es = a->dtype == APK_E4M3 ? 1 : 2;
   const uint64_t rows = (uint64_t)a->rows_per_rank * (uint64_t)comm->world;
   const uint64_t gathered = rows * (uint64_t)a->K * es;
   const uint64_t ctrl = apk_ctrl_bytes(a->rows_per_rank, comm->world);

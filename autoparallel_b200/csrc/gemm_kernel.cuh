@@ -25,6 +25,7 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -69,6 +70,8 @@ struct alignas(64) KParams {
   void* out[MAX_B];
   int64_t ldo[MAX_B];
   int32_t out_fp32[MAX_B];
+  int32_t out_f16[MAX_B];      // 16-bit outputs are IEEE half instead of bf16
+  int32_t in_f16;              // A and B are IEEE half instead of bf16 (kind::f16 takes either)
   int32_t out_tma[MAX_B];      // tmOut[b] is valid
   // ---- scaled (fp8) epilogue
   int32_t a_scale_mode;        // 0 none, 1 one scalar, 2 one per row
@@ -378,9 +381,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// Two fp32 values rounded to one 32-bit pair of bf16 (f16 == false) or IEEE half.
+__device__ __forceinline__ uint32_t pack16(float lo, float hi, bool f16) {
+  if (f16) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  return pack_bf16(lo, hi);
+}
 
 // Writes `nvalid` (multiple of 8 for bf16, 4 for fp32; <= 32) consecutive outputs of one row.
-__device__ __forceinline__ void store_row32(void* dst, const float (&v)[32], int nvalid, bool fp32) {
+__device__ __forceinline__ void store_row32(void* dst, const float (&v)[32], int nvalid, bool fp32, bool f16 = false) {
   if (fp32) {
     float4* d = reinterpret_cast<float4*>(dst);
 #pragma unroll
@@ -393,10 +404,10 @@ __device__ __forceinline__ void store_row32(void* dst, const float (&v)[32], int
     for (int j = 0; j < 4; ++j) {
       if (j * 8 < nvalid) {
         uint4 q;
-        q.x = pack_bf16(v[8 * j + 0], v[8 * j + 1]);
-        q.y = pack_bf16(v[8 * j + 2], v[8 * j + 3]);
-        q.z = pack_bf16(v[8 * j + 4], v[8 * j + 5]);
-        q.w = pack_bf16(v[8 * j + 6], v[8 * j + 7]);
+        q.x = pack16(v[8 * j + 0], v[8 * j + 1], f16);
+        q.y = pack16(v[8 * j + 2], v[8 * j + 3], f16);
+        q.z = pack16(v[8 * j + 4], v[8 * j + 5], f16);
+        q.w = pack16(v[8 * j + 6], v[8 * j + 7], f16);
         d[j] = q;
       }
     }
@@ -651,7 +662,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       const uint64_t desc_kmajor = desc_common | (uint64_t(1) << 16);
       const uint64_t desc_nmajor = desc_common | (uint64_t((BKE * ROW_BYTES) >> 4) << 16);
       // Instruction descriptor: fp32 accumulate, A/B format (bf16 = 1, e4m3 = 0), M = 128.
-      const uint32_t fmt = FP8 ? 0u : 1u;
+      const uint32_t fmt = (FP8 || p.in_f16) ? 0u : 1u;   // kind::f16: 0 = half, 1 = bf16; kind::f8f6f4: 0 = e4m3
       const uint32_t idesc_base = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t((PAIR ? 2 * BM : BM) >> 4) << 24);
       uint32_t lt = 0;  // local tile counter
       const bool tracing = p.trace != nullptr;
@@ -888,6 +899,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
 
 
       const bool o32 = p.out_fp32[b] != 0;
+      const bool o16h = p.out_f16[b] != 0;
       const int oes = o32 ? 4 : 2;
       const uint32_t t_row = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
       const bool rs_remote = (p.mode == MODE_RS) && !own;
@@ -1018,7 +1030,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
           }
           if (use_tma) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) packed[hf][j] = pack_bf16(v[2 * j], v[2 * j + 1]);
+            for (int j = 0; j < 16; ++j) packed[hf][j] = pack16(v[2 * j], v[2 * j + 1], o16h);
           } else if (row_ok) {
             uint8_t* dst;
             if (rs_remote) {
@@ -1028,7 +1040,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
             } else {
               dst = reinterpret_cast<uint8_t*>(p.out[b]) + ((size_t)grow * p.ldo[b] + col0) * oes;
             }
-            store_row32(dst, v, nvalid, o32);
+            store_row32(dst, v, nvalid, o32, o16h);
           }
         }
         if (use_tma) {

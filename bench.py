@@ -544,7 +544,7 @@ def _run_config(args, rank, world, dev, g, solo, sync_all, max_over_ranks, time_
         baselines = {"unfused_nccl_cublas": {"ag_ms": time_call(uag, 10), "rs_ms": time_call(urs, 10),
                                              "what": "all_gather_into_tensor + torch.mm / _scaled_mm; mm + reduce_scatter_tensor (NCCL)"},
                      "reference_cuda_path": {"unavailable": "the reference package cannot be installed offline (its build backend, "
-                                             "hatchling, is absent) and its source tree is not on the GPU box"}}
+                                             "hatchling, is absent), so its sources are not where this benchmark runs"}}
 
     # ---- a loop of at least two seconds: the clock settles under the power cap
     sustained = None

@@ -42,7 +42,7 @@ enum {
   APK_ERR_TIMEOUT = -4, /* a device-side wait ran out (reported by apk_check_status) */
 };
 
-enum { APK_BF16 = 0, APK_E4M3 = 1, APK_F32 = 2 };
+enum { APK_BF16 = 0, APK_E4M3 = 1, APK_F32 = 2, APK_F16 = 3 };
 
 /* How a scale operand is laid out. */
 enum {
@@ -92,7 +92,7 @@ typedef struct {
   int32_t N;
   void* out;             /* AG: [world*rows_per_rank, N]; RS: [M/world, N] */
   int64_t ldo;
-  int32_t out_dtype;     /* APK_BF16 or APK_F32 */
+  int32_t out_dtype;     /* APK_BF16, APK_F16 or APK_F32 (apk_gemm_rs with peers: not APK_F16, the partials travel as bf16 or f32) */
   int32_t b_scale_mode;  /* APK_SCALE_NONE / SCALAR / VECTOR (per column) */
   const float* b_scale;
   const void* bias;      /* per column, or null */
@@ -107,7 +107,7 @@ typedef struct {
  * moved gather_dim to the front and flattened A to 2-D (:437-443).
  */
 typedef struct {
-  int32_t dtype;          /* APK_BF16 or APK_E4M3: element type of A and every B */
+  int32_t dtype;          /* APK_BF16, APK_F16 or APK_E4M3: element type of A and every B */
   int32_t rows_per_rank;  /* rows of A_shard */
   int32_t K;
   int32_t nB;

@@ -23,8 +23,8 @@ import torch.distributed as dist
 
 from autoparallel_b200 import _native as nat
 
-_IN = {nat.APK_BF16: torch.bfloat16, nat.APK_E4M3: torch.float8_e4m3fn}
-_OUT = {nat.APK_BF16: torch.bfloat16, nat.APK_F32: torch.float32}
+_IN = {nat.APK_BF16: torch.bfloat16, nat.APK_E4M3: torch.float8_e4m3fn, nat.APK_F16: torch.float16}
+_OUT = {nat.APK_BF16: torch.bfloat16, nat.APK_F32: torch.float32, nat.APK_F16: torch.float16}
 
 
 def _bytes(addr: int, nbytes: int) -> torch.Tensor:

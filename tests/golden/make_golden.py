@@ -1,6 +1,6 @@
 """Generates tests/golden/asynctp_golden.pt by running the REFERENCE's own unfused fallbacks.
 
-Run in a container that has the AutoParallel sources (they do not travel to the GPU box):
+Run where the AutoParallel sources are available (the fixtures it writes are what travels with this repository):
 
     python tests/golden/make_golden.py /path/to/autoparallel_checkout
 
@@ -104,7 +104,9 @@ def _worker(rank, ref_root, initfile, outdir):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("AUTOPARALLEL_REFERENCE", "")
+    if not os.path.isdir(ref_root):
+        raise SystemExit("usage: pass the AutoParallel source tree as the first argument (or in $AUTOPARALLEL_REFERENCE)")
     with tempfile.TemporaryDirectory() as d:
         initfile = os.path.join(d, "init")
         mp.spawn(_worker, args=(ref_root, initfile, d), nprocs=WORLD, join=True)

@@ -22,6 +22,7 @@ Two groups of cases, marked by ``scaled_mm`` in every record:
   results, ``output_shape`` and the reduce-scatter. The row-wise arithmetic itself is checked
   against ``torch._scaled_mm`` on a GPU by the gpu tests.
 """
+import os
 import sys
 import threading
 import traceback
@@ -110,7 +111,9 @@ def _run_case(ref, ci, c, rank, g):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("AUTOPARALLEL_REFERENCE", "")
+    if not os.path.isdir(ref_root):
+        raise SystemExit("usage: pass the AutoParallel source tree as the first argument (or in $AUTOPARALLEL_REFERENCE)")
     sys.path.insert(0, ref_root)
     import autoparallel.asynctp_ops as ref
     from torch.testing._internal.distributed.multi_threaded_pg import _install_threaded_pg, _uninstall_threaded_pg

@@ -19,7 +19,8 @@ import torch.distributed as dist
 import autoparallel_b200.asynctp_ops as ops
 from autoparallel_b200.install import install
 
-REFERENCE = os.environ.get("AUTOPARALLEL_REFERENCE", "/root/reference")
+# The AutoParallel source tree: $AUTOPARALLEL_REFERENCE, or a checkout named `reference` beside this repository.
+REFERENCE = os.environ.get("AUTOPARALLEL_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 pytestmark = pytest.mark.skipif(not os.path.isdir(REFERENCE), reason="AutoParallel sources not present")
 
 BF, F8, F32 = torch.bfloat16, torch.float8_e4m3fn, torch.float32

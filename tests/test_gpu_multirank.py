@@ -190,6 +190,18 @@ def _worker(rank, world, golden, golden_fp8):
     )[rank]
     assert out.shape == ref.shape and orc.rel_fro_error(out, ref.double()) <= FP8_TOL
 
+    # ---- float16 operands: the all-gather as is, the reduce-scatter with fp32 partials rounded once at the end
+    hs = [orc.activations(130 + r, 384, 520, torch.float16) for r in range(world)]
+    Bh = orc.weights(131, 520, 264, torch.float16, std=0.05)
+    A_out, (o,) = ns.fused_all_gather_matmul(hs[rank].to(dev), [Bh.to(dev)], 0, g)
+    assert o.dtype == torch.float16 and torch.equal(A_out.cpu(), torch.cat(hs))
+    assert err(o, lambda: d64(torch.cat(hs)) @ d64(Bh)) <= BF16_TOL / 4
+    Xh = [orc.activations(140 + r, 256 * world, 520, torch.float16) for r in range(world)]
+    out = ns.fused_matmul_reduce_scatter(Xh[rank].to(dev), Bh.to(dev), "sum", 0, g)
+    lo, hi = rank * 256, (rank + 1) * 256
+    assert out.dtype == torch.float16 and out.shape == (256, 264)
+    assert err(out, lambda: sum(d64(x[lo:hi]) for x in Xh) @ d64(Bh)) <= BF16_TOL / 4
+
     # ---- stand-alone collectives over the same arena and flags
     x = orc.activations(110 + rank, 300, 264).to(dev)
     got = ns._low_contention_all_gather(x, g)

@@ -483,6 +483,29 @@ def test_more_than_four_operands(group):
         assert orc.rel_fro_error(o, A.double() @ b.double()) <= BF16_TOL
 
 
+@pytest.mark.parametrize("b_layout", ["row_major", "transposed_view"])
+def test_float16_operands(group, b_layout):
+    """float16 A and B (the reference forwards any dtype to aten.mm, autoparallel/asynctp_ops.py:519, :1168):
+    same kernels, IEEE-half operand format and outputs. Tolerance as for bf16; half has three more mantissa bits."""
+    g = torch.Generator(device="cuda").manual_seed(11)
+    A = torch.randn(1000, 1032, device="cuda", generator=g).half()
+    Bs = [(torch.randn(1032, n, device="cuda", generator=g) * 0.05).half() for n in (264, 512)]
+    if b_layout == "transposed_view":
+        Bs = [b.t().contiguous().t() for b in Bs]
+    A_out, outs = torch.ops._ap_symm_mem.fused_all_gather_matmul(A, Bs, 0, group)
+    assert torch.equal(A_out, A)
+    for o, b in zip(outs, Bs):
+        assert o.dtype == torch.float16
+        e = ((o.double() - A.double() @ b.double()).norm() / (A.double() @ b.double()).norm()).item()
+        assert e <= BF16_TOL / 4, e
+        lib = A @ b                       # cuBLAS, fp32 accumulate, rounded to half
+        assert ((o.double() - lib.double()).norm() / lib.double().norm()).item() <= 2 ** -10
+    w2 = (torch.randn(264, 520, device="cuda", generator=g) * 0.05).half()
+    out = torch.ops._ap_symm_mem.fused_matmul_reduce_scatter(outs[0], w2, "avg", 0, group)
+    ref = outs[0].double() @ w2.double()
+    assert out.dtype == torch.float16 and ((out.double() - ref).norm() / ref.norm()).item() <= BF16_TOL / 4
+
+
 def test_timeline_stamps_are_ordered(group):
     """apk_set_trace: every tile of a launch leaves one record, and inside a record the stamps follow the
     pipeline: first load <= first MMA <= last MMA committed <= accumulator complete <= epilogue done, all

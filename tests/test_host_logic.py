@@ -10,7 +10,8 @@ import torch.distributed as dist
 import autoparallel_b200.asynctp_ops as ops
 from autoparallel_b200.install import install
 
-REFERENCE = os.environ.get("AUTOPARALLEL_REFERENCE", "/root/reference")
+# The AutoParallel source tree: $AUTOPARALLEL_REFERENCE, or a checkout named `reference` beside this repository.
+REFERENCE = os.environ.get("AUTOPARALLEL_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 
 
 @pytest.fixture(scope="module")
@@ -116,7 +117,7 @@ def test_argument_errors_match_reference(fake_pg):
         ops._ag_gemm_native(A, [B], None, n, n, n, [], 0, g, True)
     with pytest.raises(ValueError, match="gathered A has 512 columns"):   # last-dim gather: B must span all K-slices
         ops._ag_gemm_native(A, [B], None, n, n, n, [bf], 1, g, True)
-    with pytest.raises(NotImplementedError, match="bfloat16 or float8_e4m3fn"):
+    with pytest.raises(NotImplementedError, match="bfloat16, float16 or float8_e4m3fn"):
         ops._ag_gemm_native(A.float(), [B.float()], None, n, n, n, [torch.float32], 0, g, True)
     with pytest.raises(ValueError, match="reduce_op must be sum or avg"):
         ops._check_reduce_op("max")

@@ -185,3 +185,18 @@ def test_empty_inputs_are_not_collectives(recorder):
     assert tuple(out.shape) == (0, 8)
     assert not rec.ag and not rec.rs
     assert g not in symm._workspaces or symm._workspaces[g].epoch == 0
+
+
+def test_float16_operands(recorder):
+    """float16 operands go to the same kernels (kind::f16 takes either 16-bit format). With peers a float16
+    reduce-scatter is computed with fp32 partials and rounded once at the end."""
+    rec, g = recorder
+    h = torch.float16
+    A_out, (o,) = ops._fused_all_gather_matmul(torch.zeros(16, 64, dtype=h), [torch.zeros(64, 40, dtype=h)], 0, g)
+    (_, a), = rec.ag
+    assert (a.dtype, a.Bs[0].out_dtype) == (nat.APK_F16, nat.APK_F16) and o.dtype == h and A_out.dtype == h
+    out = ops._fused_matmul_reduce_scatter(torch.zeros(64, 64, dtype=h), torch.zeros(64, 40, dtype=h), "sum", 0, g)
+    r = rec.rs[-1]
+    assert (r.dtype, r.B.out_dtype) == (nat.APK_F16, nat.APK_F32) and out.dtype == h and tuple(out.shape) == (8, 40)
+    with pytest.raises(NotImplementedError, match="float16"):
+        ops._fused_all_gather_matmul(torch.zeros(16, 64), [torch.zeros(64, 40)], 0, g)     # fp32 operands: no tensor-core format
