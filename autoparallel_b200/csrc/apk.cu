@@ -115,10 +115,10 @@ int device_info(DeviceInfo* out) {
 // when the occupancy query or the launch itself says that clusters of two are not schedulable.
 char g_pair_unsupported[kMaxDevices][160] = {};
 
-template <int BN, int STAGES, bool FP8, bool PAIR>
-int launch_instance(apk::KParams kp, long long units, const DeviceInfo& di, cudaStream_t stream) {
+template <int BN, int STAGES, bool FP8, bool PAIR, bool TRACE>
+int launch_instance_t(apk::KParams kp, long long units, const DeviceInfo& di, cudaStream_t stream) {
   using L = apk::SmemLayout<BN, STAGES, PAIR>;
-  auto kern = apk::gemm_fused_kernel<BN, STAGES, FP8, PAIR>;
+  auto kern = apk::gemm_fused_kernel<BN, STAGES, FP8, PAIR, TRACE>;
   static bool configured[kMaxDevices] = {};
   static int max_clusters[kMaxDevices] = {};
   int dev = 0;
@@ -179,7 +179,7 @@ int launch_instance(apk::KParams kp, long long units, const DeviceInfo& di, cuda
   // Timeline: one record per (CTA, local tile), only when the buffer set by apk_set_trace is large enough.
   kp.trace = nullptr;
   kp.trace_tiles = 0;
-  if (g_trace != nullptr && g_trace_device == dev) {
+  if (TRACE && g_trace != nullptr && g_trace_device == dev) {
     const long long sched_ctas = PAIR ? cfg.gridDim.x / 2 : cfg.gridDim.x;
     const long long per_cta = (units + sched_ctas - 1) / sched_ctas;
     const uint64_t need = (uint64_t)cfg.gridDim.x * (uint64_t)per_cta * apk::TRACE_FIELDS * 8;
@@ -200,6 +200,20 @@ int launch_instance(apk::KParams kp, long long units, const DeviceInfo& di, cuda
   g_launches.fetch_add(1);
   if (PAIR) g_pair_launches.fetch_add(1);
   return APK_OK;
+}
+
+// The instances with the timeline compiled in are used only while a timeline buffer is set for this device.
+template <int BN, int STAGES, bool FP8, bool PAIR>
+int launch_instance(const apk::KParams& kp, long long units, const DeviceInfo& di, cudaStream_t stream) {
+  int dev = -1;
+  cudaGetDevice(&dev);
+  bool tracing;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    tracing = g_trace != nullptr && g_trace_device == dev;
+  }
+  return tracing ? launch_instance_t<BN, STAGES, FP8, PAIR, true>(kp, units, di, stream)
+                 : launch_instance_t<BN, STAGES, FP8, PAIR, false>(kp, units, di, stream);
 }
 
 // CTA pairs (cta_group::2) are used when every output is a whole number of 256-column tiles and every

@@ -467,7 +467,11 @@ __device__ __forceinline__ void copy_piece(const uint8_t* src, uint8_t* dst, uin
 // rank 0. Each CTA loads its own 128 rows of A and HALF of B's columns (32 KiB instead of 48 KiB
 // per k-block from L2, the bound of the single-CTA kernel), keeps its 128 x BN accumulator in its
 // own TMEM and runs its own epilogue and communication warps exactly as without PAIR.
-template <int BN, int STAGES, bool FP8, bool PAIR>
+// TRACE: the timeline instrumentation is compiled in. It is a template parameter and not a run-time test
+// because the MMA-issuing thread sets the pace of the kernel: a few extra instructions in its loop, even
+// never-taken branches, cost several percent of the whole GEMM (measured). Launches made while a timeline
+// buffer is set use the TRACE instances; all others carry none of it.
+template <int BN, int STAGES, bool FP8, bool PAIR, bool TRACE = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid_constant__ KParams p) {
   using L = SmemLayout<BN, STAGES, PAIR>;
   constexpr int BKE = FP8 ? 128 : 64;           // K elements per stage (128 bytes)
@@ -540,7 +544,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       uint32_t it = 0;       // k-block counter over the CTA's lifetime
       uint32_t pstage = 0, pphase = 0;   // = it % STAGES and (it / STAGES) & 1, kept as counters
       uint32_t lt = 0;       // local tile counter
-      const bool tracing = p.trace != nullptr;
+      constexpr bool tracing = TRACE;
       bool ok = true;
       if (tracing) {
         trace_put(p, 0, TR_CTA_BEGIN_T, globaltimer_ns());
@@ -665,7 +669,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       const uint32_t fmt = (FP8 || p.in_f16) ? 0u : 1u;   // kind::f16: 0 = half, 1 = bf16; kind::f8f6f4: 0 = e4m3
       const uint32_t idesc_base = (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t((PAIR ? 2 * BM : BM) >> 4) << 24);
       uint32_t lt = 0;  // local tile counter
-      const bool tracing = p.trace != nullptr;
+      constexpr bool tracing = TRACE;
       bool ok = true;
       // The loop below is kept short on purpose (see ReleaseEvery): stage and phase are running counters,
       // the barrier addresses of both CTAs are computed once, and the next stage's `full` barrier is
@@ -764,7 +768,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
     uint32_t stg_count = 0;
     bool prev_coop = false;   // the previous tile left as cooperative 16 KiB copies issued by the leader
     uint32_t lt = 0;
-    const bool tracing = p.trace != nullptr;
+    constexpr bool tracing = TRACE;
     // Reduce-scatter: tiles sent to their owners and not yet announced, oldest first (the same
     // values in all 4 warps). Up to four tiles stay in flight and flags are released two tiles at
     // a time behind ONE system-scope fence: a fence costs a round trip over a busy NVLink, so it
@@ -1112,7 +1116,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       const size_t src_stride = (size_t)sched.tiles_per_chunk * (BN / 64) * 4 * (32 * ROW_BYTES);
       uint32_t done = 0;
       uint32_t lt = 0;
-      const bool tracing = p.trace != nullptr;
+      constexpr bool tracing = TRACE;
       for (int t = tile_first; t < sched.total_tiles; t += tile_step, ++lt) {
         const TileInfo ti = decode_tile<BN, PAIR>(p, sched, t, crank);
         if (ti.chunk != p.rank) continue;
@@ -1306,7 +1310,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
   // ============================================================ teardown
   ptx::tc_fence_before();
   if (PAIR) ptx::cluster_sync(); else __syncthreads();   // pair: nobody signals a CTA that has left
-  if (threadIdx.x == 0 && p.trace != nullptr) {
+  if (TRACE && threadIdx.x == 0) {
     trace_put(p, 0, TR_CTA_END_T, globaltimer_ns());
     trace_put(p, 1, TR_CTA_END_T, (unsigned long long)clock64());
   }

@@ -36,6 +36,11 @@ from . import _native as nat
 
 FLAG_PAD_BYTES = 4096 + 4 * nat.APK_MAX_WORLD * 65536  # staged flags + 65536 tile flags per source rank
 DEFAULT_TIMEOUT_S = 30.0
+# Guard zones in front of and behind the data arena and the signal pad, filled with a pattern at allocation and
+# compared in check_guards(): a kernel (local or a peer's, the zones are part of the peer-mapped allocation) that
+# writes outside the arena it was given shows up here. Stands in for a memory checker where none can be run.
+GUARD_BYTES = 4096
+GUARD_WORD = 0x5AFEC0DE   # below 2**31: the same value as a signed 32-bit word
 
 
 def _capturing() -> bool:
@@ -75,8 +80,9 @@ class GroupWorkspace:
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
         self.ctrl = torch.zeros(1024, dtype=torch.int32, device=device)
         self.handles = PeerHandles(self.rank, self.world)
-        self._local_data = 0
+        self._local_data = 0        # base addresses of the local allocations (guard zones included)
         self._local_flags = 0
+        self._local_sizes = (0, 0)  # usable bytes of the arena and of the pad
         self._imported: list[int] = []
 
     # ------------------------------------------------------------------ allocation
@@ -130,13 +136,16 @@ class GroupWorkspace:
         need = max(need, 2 * self.handles.data_bytes)
         with torch.cuda.device(self.device):
             p = C.c_void_p()
-            nat.check(L.apk_symm_alloc(need, C.byref(p)))
+            nat.check(L.apk_symm_alloc(need + 2 * GUARD_BYTES, C.byref(p)))
             self._local_data = p.value
             f = C.c_void_p()
-            nat.check(L.apk_symm_alloc(FLAG_PAD_BYTES, C.byref(f)))
+            nat.check(L.apk_symm_alloc(FLAG_PAD_BYTES + 2 * GUARD_BYTES, C.byref(f)))
             self._local_flags = f.value
-            self.handles.data = self._exchange(self._local_data)
-            self.handles.flags = self._exchange(self._local_flags)
+            self._local_sizes = (need, FLAG_PAD_BYTES)
+            self._fill_guards()
+            # what the kernels see starts behind the leading guard zone, on every rank alike
+            self.handles.data = [a + GUARD_BYTES for a in self._exchange(self._local_data)]
+            self.handles.flags = [a + GUARD_BYTES for a in self._exchange(self._local_flags)]
         self.handles.data_bytes = need
         self.handles.flag_bytes = FLAG_PAD_BYTES
         # A zero-filled pad starts a new epoch sequence (all ranks grow in the same call, so they
@@ -144,6 +153,41 @@ class GroupWorkspace:
         # than 2**31 ops apart, and zeros next to an old epoch count need not be.
         self.epoch = 0
         dist.barrier(group=self.group)
+
+    # ------------------------------------------------------------------ guard zones and flag sanity
+    def _guard_views(self) -> list[torch.Tensor]:
+        """The four guard zones of the local allocations as int32 device tensors (empty list before allocation)."""
+        out = []
+        for base, size in zip((self._local_data, self._local_flags), self._local_sizes):
+            if base:
+                for addr in (base, base + GUARD_BYTES + size):
+                    out.append(_device_int32_view(addr, GUARD_BYTES // 4, self.device))
+        return out
+
+    def _fill_guards(self) -> None:
+        for v in self._guard_views():
+            v.fill_(GUARD_WORD)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+
+    def check_guards(self) -> None:
+        """Raise if anything was written in front of or behind the arena or the signal pad, or if a 'staged'
+        flag holds a value that no op of this group can have written yet (flags only ever carry epochs that
+        have been reached: a larger value means a stray write or a confused epoch sequence)."""
+        names = ("before the data arena", "behind the data arena", "before the signal pad", "behind the signal pad")
+        want = GUARD_WORD
+        for name, v in zip(names, self._guard_views()):
+            bad = (v != want).nonzero()
+            if bad.numel():
+                raise RuntimeError(
+                    f"group {self.group_name!r}: guard zone {name} was overwritten "
+                    f"({bad.numel()} words, first at byte offset {int(bad[0]) * 4})")
+        if self._local_flags:
+            staged = _device_int32_view(self._local_flags + GUARD_BYTES, 1024, self.device).cpu()
+            ahead = ((staged.to(torch.int64) - self.epoch + (1 << 31)) % (1 << 32)) - (1 << 31)   # wrap-safe flag - epoch
+            if bool((ahead > 0).any()):
+                raise RuntimeError(
+                    f"group {self.group_name!r}: a 'staged' flag is {int(ahead.max())} ahead of the group's epoch {self.epoch}")
 
     # ------------------------------------------------------------------ per call
     def next_comm(self) -> nat.ApkComm:
@@ -192,8 +236,24 @@ class GroupWorkspace:
         nat.check(nat.lib().apk_check_status(C.byref(c), C.c_void_p(stream), C.byref(raw)))
 
     def close(self) -> None:
+        if self._local_data or self._local_flags:
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            self.check_guards()
         self._release()
+        self._local_sizes = (0, 0)
         self.handles = PeerHandles(self.rank, self.world)
+
+
+def _device_int32_view(addr: int, n: int, device: torch.device) -> torch.Tensor:
+    """`n` int32 words of memory at `addr` as a tensor on `device` (no copy, no ownership)."""
+    if device.type == "cpu":   # host-memory stand-ins of the allocator (CPU tests)
+        return torch.frombuffer((C.c_int32 * n).from_address(addr), dtype=torch.int32)
+
+    class _Span:   # the CUDA array interface torch understands
+        __cuda_array_interface__ = {"shape": (n,), "typestr": "<i4", "data": (addr, False), "version": 2}
+
+    return torch.as_tensor(_Span(), device=device)
 
 
 _workspaces: dict[str, GroupWorkspace] = {}
@@ -220,6 +280,7 @@ def sync_check(group_name: str | None = None) -> None:
     for name, ws in _workspaces.items():
         if group_name is None or name == group_name:
             ws.check_status()
+            ws.check_guards()
 
 
 def shutdown() -> None:

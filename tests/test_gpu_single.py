@@ -281,7 +281,7 @@ def test_empty_and_errors(group):
         torch.ops._ap_symm_mem.fused_matmul_reduce_scatter(X, B, "max", 0, group)
     with pytest.raises(ValueError, match="Invalid gather_dim"):
         torch.ops._ap_symm_mem.fused_all_gather_matmul(X, [B], 3, group)
-    with pytest.raises(NotImplementedError, match="bfloat16 or float8_e4m3fn"):
+    with pytest.raises(NotImplementedError, match="bfloat16, float16 or float8_e4m3fn"):
         torch.ops._ap_symm_mem.fused_all_gather_matmul(X.float(), [B.float()], 0, group)
     from autoparallel_b200._native import ApkError
 

@@ -136,3 +136,33 @@ def test_device_timeout_surfaces_as_an_exception_and_keeps_the_epoch(group):
         symm.sync_check(g)
     assert e.value.code == nat.APK_ERR_TIMEOUT
     assert w.epoch == before              # reading the status is not a collective
+
+
+def test_guard_zones_catch_writes_outside_the_arena(group, monkeypatch):
+    """The arena and the signal pad sit between guard zones filled with a pattern; anything written there, or a
+    'staged' flag that is ahead of the group's epoch, is reported by the next sync_check()."""
+    import ctypes as C
+
+    import contextlib
+
+    fake, g = group
+    monkeypatch.setattr(torch.cuda, "device", lambda *a, **k: contextlib.nullcontext())
+    monkeypatch.setattr(dist, "barrier", lambda *a, **k: None)
+    monkeypatch.setattr(dist, "all_gather_object", lambda out, obj, group=None: [out.__setitem__(i, obj) for i in range(len(out))])
+    w = symm.get_workspace(g, torch.device("cpu"))
+    w.ensure(1 << 16, 256)
+    data_base, flags_base = w._local_data, w._local_flags
+    assert w.handles.data[w.rank] == data_base + symm.GUARD_BYTES      # kernels start behind the leading zone
+    assert w.handles.flags[w.rank] == flags_base + symm.GUARD_BYTES
+    w.next_comm()
+    w.check_guards()                                                   # untouched: fine
+    C.c_uint32.from_address(data_base + symm.GUARD_BYTES + w.handles.data_bytes + 8).value = 7     # one word behind the arena
+    with pytest.raises(RuntimeError, match="behind the data arena"):
+        w.check_guards()
+    C.c_uint32.from_address(data_base + symm.GUARD_BYTES + w.handles.data_bytes + 8).value = symm.GUARD_WORD
+    w.check_guards()
+    C.c_uint32.from_address(flags_base + symm.GUARD_BYTES + 128).value = w.epoch + 5               # a flag from the future
+    with pytest.raises(RuntimeError, match="ahead of the group's epoch"):
+        w.check_guards()
+    C.c_uint32.from_address(flags_base + symm.GUARD_BYTES + 128).value = w.epoch
+    w.check_guards()
