@@ -53,6 +53,7 @@ EXPORTED_SYMBOLS = (
     "apk_all_gather",
     "apk_reduce_scatter",
     "apk_debug_schedule",
+    "apk_debug_set_rs_lag",
     "apk_check_status",
     "apk_launch_count",
     "apk_pair_launch_count",
@@ -174,6 +175,8 @@ def lib() -> C.CDLL:
     L.apk_reduce_scatter.restype = C.c_int
     L.apk_debug_schedule.argtypes = [C.c_int32] * 5 + [C.POINTER(C.c_int32)] + [C.c_int32] * 3 + [C.POINTER(C.c_int32), C.c_int32]
     L.apk_debug_schedule.restype = C.c_int
+    L.apk_debug_set_rs_lag.argtypes = [C.c_int32]
+    L.apk_debug_set_rs_lag.restype = None
     L.apk_check_status.argtypes = [C.POINTER(ApkComm), C.c_void_p, C.POINTER(C.c_uint32)]
     L.apk_launch_count.restype = C.c_uint64
     L.apk_pair_launch_count.restype = C.c_uint64

@@ -763,6 +763,9 @@ int apk_reduce_scatter(const apk_comm* comm, const void* in, void* out, uint64_t
   return launch_collective(apk::reduce_scatter_kernel, cp, stream);
 }
 
+static int g_debug_rs_lag = 0;
+void apk_debug_set_rs_lag(int32_t row_blocks) { g_debug_rs_lag = row_blocks; }
+
 int apk_debug_schedule(int32_t mode, int32_t world, int32_t rank, int32_t rows_per_rank, int32_t nB, const int32_t* N,
                        int32_t last_dim, int32_t pair, int32_t crank, int32_t* out, int32_t capacity) {
   if (nB < 1 || nB > APK_MAX_B || N == nullptr || world < 1 || world > APK_MAX_WORLD) return fail(APK_ERR_ARG, "bad arguments");
@@ -775,6 +778,7 @@ int apk_debug_schedule(int32_t mode, int32_t world, int32_t rank, int32_t rows_p
   kp.rows_per_rank = rows_per_rank;
   kp.ag_ksplit = (mode == apk::MODE_AG && last_dim) ? 1 : 0;
   kp.rs_colsplit = (mode == apk::MODE_RS && last_dim) ? 1 : 0;
+  kp.rs_lag = g_debug_rs_lag;
   int max_n = 0;
   for (int b = 0; b < nB; ++b) {
     kp.N[b] = N[b];

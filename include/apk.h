@@ -212,6 +212,10 @@ int apk_check_status(const apk_comm* comm, void* stream, uint32_t* raw);
 int apk_debug_schedule(int32_t mode, int32_t world, int32_t rank, int32_t rows_per_rank, int32_t nB, const int32_t* N,
                        int32_t last_dim, int32_t pair, int32_t crank, int32_t* out, int32_t capacity);
 
+/* Test utility: the reduce-scatter lag (row blocks between the peers' row block j and the own one) that
+ * apk_debug_schedule uses from now on; 0 = the built-in default. Real launches compute theirs from the grid. */
+void apk_debug_set_rs_lag(int32_t row_blocks);
+
 /* Kernels launched by this library in this process so far (memsets not counted). */
 uint64_t apk_launch_count(void);
 /* ... of which launched as clusters of two CTAs (tcgen05 cta_group::2). */

@@ -148,8 +148,8 @@ def test_every_tile_is_scheduled_exactly_once(shape):
 
 
 @settings(max_examples=60, deadline=None)
-@given(_shapes(modes=(RS,)))
-def test_reduce_scatter_waits_only_on_earlier_positions(shape):
+@given(_shapes(modes=(RS,)), st.sampled_from([0, 1, 2, 5, 14, 40]))
+def test_reduce_scatter_waits_only_on_earlier_positions(shape, lag):
     """Progress argument of the reduce-scatter: a unit that owns its tile waits for the peers'
     partials of the same tile. On every peer that tile sits at an EARLIER position of the peer's
     list, and sends never wait on anything, so by induction over positions no set of co-resident
@@ -157,7 +157,14 @@ def test_reduce_scatter_waits_only_on_earlier_positions(shape):
     mode, world, rank, rows, Ns, last_dim, pair = shape
     if world == 1:
         return
-    per_rank = [_units(mode, world, r, rows, Ns, last_dim, pair) for r in range(world)]
+    build_native()
+    nat.lib().apk_debug_set_rs_lag(lag)       # launches size the lag from the grid; every value must keep the order safe
+    try:
+        per_rank = [_units(mode, world, r, rows, Ns, last_dim, pair) for r in range(world)]
+    finally:
+        nat.lib().apk_debug_set_rs_lag(0)
+    want = expected_tiles(world, rows, Ns, 128 if max(Ns) <= 128 else 256, range(world))
+    assert all({t[:4] for u in units for t in u} == want for units in per_rank)      # still an exact cover
     pos = [{t[:4]: i for i, u in enumerate(units) for t in u} for units in per_rank]
     ident = [{t[:4]: t[4] for u in units for t in u} for units in per_rank]
     for r in range(world):
