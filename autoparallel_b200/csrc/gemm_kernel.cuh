@@ -659,7 +659,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
     __syncwarp();
   } else if (warp == 1) {
     // ============================================================ MMA issuer
-    if (lane == 0 && crank == 0) {
+    // The whole warp walks the loop (waits, stage bookkeeping and descriptor arithmetic are the same in all
+    // lanes, so they can stay in the uniform datapath) and ONE elected lane issues the tcgen05 instructions:
+    // with the loop inside a single-lane branch every operand of every MMA had to be moved over from that
+    // lane's registers first.
+    if (crank == 0) {
       // Shared-memory matrix descriptor: version 1 (bit 46), 128-byte swizzle (2 << 61),
       // stride byte offset 1024 (8 rows x 128 B) in 16-byte units at bit 32.
       const uint64_t desc_common = (uint64_t(1) << 46) | (uint64_t(2) << 61) | (uint64_t(1024 >> 4) << 32);
@@ -678,9 +682,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
       const uint32_t full0 = full_bar(0);
       const uint32_t empty_c0 = PAIR ? ptx::mapa(empty_bar(0), 0) : empty_bar(0);
       const uint32_t empty_c1 = PAIR ? ptx::mapa(empty_bar(0), 1) : 0u;
+      const uint32_t tfull_c0 = PAIR ? ptx::mapa(tfull_bar(0), 0) : tfull_bar(0);
+      const uint32_t tfull_c1 = PAIR ? ptx::mapa(tfull_bar(0), 1) : 0u;
       const uint32_t a_lo0 = (smem_base >> 4) & 0x3fffu;
       const uint32_t b_lo0 = ((smem_base + L::A_BYTES) >> 4) & 0x3fffu;
-      bool ready = ptx::mbar_test_wait(full0, 0u);
+      // every decision that steers the loop is made warp-uniform (votes), so that all lanes reach every elect
+      bool ready = __all_sync(0xffffffffu, ptx::mbar_test_wait(full0, 0u));
       for (int t = tile_first; t < sched.total_tiles && ok; t += tile_step, ++lt) {
         const TileInfo ti = decode_tile<BN, PAIR>(p, sched, t, crank);
         const uint32_t acc = lt & 1u;
@@ -688,8 +695,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
         long long tr_full = 0;
         {
           const long long c0 = tracing ? clock64() : 0;
-          ok = mbar_wait(tempty_bar(acc), aph ^ 1u, p, abort_flag);
-          if (tracing) trace_put(p, lt, TR_TEMPTY_WAIT, (unsigned long long)(clock64() - c0));
+          ok = __all_sync(0xffffffffu, mbar_wait(tempty_bar(acc), aph ^ 1u, p, abort_flag));
+          if (tracing && lane == 0) trace_put(p, lt, TR_TEMPTY_WAIT, (unsigned long long)(clock64() - c0));
         }
         if (!ok) break;
         ptx::tc_fence_after();
@@ -702,17 +709,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!ready) {
             const long long c0 = tracing ? clock64() : 0;
-            ok = mbar_wait(full0 + 8u * stage, phase, p, abort_flag);
+            ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8u * stage, phase, p, abort_flag));
             if (tracing) tr_full += clock64() - c0;
             if (!ok) break;
           }
-          if (tracing && kb == 0) trace_put(p, lt, TR_MMA_T, globaltimer_ns());
+          if (tracing && kb == 0 && lane == 0) trace_put(p, lt, TR_MMA_T, globaltimer_ns());
           ptx::tc_fence_after();
           const uint32_t s = stage;
           if (++stage == (uint32_t)STAGES) { stage = 0; phase ^= 1u; }
-          ready = ptx::mbar_test_wait(full0 + 8u * stage, phase);   // the NEXT k-block's operands (may belong to the next tile)
+          ready = __all_sync(0xffffffffu, ptx::mbar_test_wait(full0 + 8u * stage, phase));   // the NEXT k-block's operands (may belong to the next tile)
           const uint64_t adesc = desc_kmajor | uint64_t(a_lo0 + s * (uint32_t)(L::STAGE_BYTES >> 4));
           const uint64_t bdesc = bdesc_hi | uint64_t(b_lo0 + s * (uint32_t)(L::STAGE_BYTES >> 4));
+          if (ptx::elect_one()) {
 #pragma unroll
           for (int k = 0; k < KSTEPS; ++k) {
             const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
@@ -733,22 +741,26 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
               ptx::tc_commit(empty_c0 + 8u * (s / RE));
             }
           }
+          }   // elected lane
         }
-        if (ok) {
+        if (ok && ptx::elect_one()) {
           if (PAIR) {
-            ptx::tc_commit_pair(ptx::mapa(tfull_bar(acc), 0));
-            ptx::tc_commit_pair(ptx::mapa(tfull_bar(acc), 1));
+            ptx::tc_commit_pair(tfull_c0 + 8u * acc);
+            ptx::tc_commit_pair(tfull_c1 + 8u * acc);
           } else {
-            ptx::tc_commit(tfull_bar(acc));
+            ptx::tc_commit(tfull_c0 + 8u * acc);
           }
         }
-        if (tracing) {
+        if (tracing && lane == 0) {
           trace_put(p, lt, TR_FULL_WAIT, (unsigned long long)tr_full);
           trace_put(p, lt, TR_COMMIT_T, globaltimer_ns());
         }
       }
-      // Make sure nothing this thread issued is still running before TMEM is freed.
-      if (PAIR) ptx::tc_commit_pair(ptx::mapa(drain_bar, 0)); else ptx::tc_commit(drain_bar);
+      // Make sure nothing the elected lane issued is still running before TMEM is freed.
+      __syncwarp();
+      if (ptx::elect_one()) {
+        if (PAIR) ptx::tc_commit_pair(ptx::mapa(drain_bar, 0)); else ptx::tc_commit(drain_bar);
+      }
       uint32_t spins = 0;
       while (!ptx::mbar_try_wait(drain_bar, 0) && ++spins < (1u << 20)) {
       }
