@@ -751,8 +751,8 @@ def _traffic_ag_bytes(cfg: dict):
 
 
 _NCU_B_BYTES = 29.36e6        # w1 + w3
-_NCU_8192_READ = 99.09e6      # dram__bytes_read.sum at 8192 tokens
-_NCU_8192_WRITE = 41.10e6     # dram__bytes_write.sum at 8192 tokens
+_NCU_8192_READ = 104.65e6     # dram__bytes_read.sum at 8192 tokens
+_NCU_8192_WRITE = 42.38e6     # dram__bytes_write.sum at 8192 tokens
 
 
 def main():
