@@ -164,3 +164,37 @@ def test_unchanged_fx_pass_targets_the_drop_in(fake_pg):
     assert torch.ops._c10d_functional.reduce_scatter_tensor.default not in targets
     ag = next(n for n in gm.graph.nodes if n.target == torch.ops._ap_symm_mem.fused_all_gather_matmul.default)
     assert len(ag.args[1]) == 2 and ag.kwargs.get("return_A") is False
+
+
+def test_torch_pass_can_be_retargeted_to_these_ops(fake_pg):
+    """torch's own micro-pipeline pass (which AutoParallel's is a fork of) inserts the same calls under
+    torch.ops.symm_mem; install.retarget_symm_mem_calls points them at this package's ops, arguments untouched.
+    (This is what tests/test_gpu_compiled_graph.py runs under torch.compile on GPUs.)"""
+    import torch.distributed._functional_collectives as funcol
+    from torch._inductor.fx_passes.micro_pipeline_tp import micro_pipeline_tp_pass
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    from torch.distributed._symmetric_memory import _test_mode
+    from torch.fx.experimental.proxy_tensor import make_fx
+
+    from autoparallel_b200.install import retarget_symm_mem_calls
+
+    g = fake_pg
+
+    def f(x, w1, w3, w2):
+        a = funcol.all_gather_tensor(x, 0, g)
+        h = torch.nn.functional.silu(a @ w1) * (a @ w3)
+        return funcol.reduce_scatter_tensor(h @ w2, "sum", 0, g)
+
+    with FakeTensorMode():
+        args = [torch.empty(s, dtype=torch.bfloat16, device="cuda") for s in ((512, 1024), (1024, 256), (1024, 256), (256, 1024))]
+        gm = make_fx(f, tracing_mode="fake")(*args)
+    with _test_mode():
+        micro_pipeline_tp_pass(gm.graph)
+    before = [str(n.args) for n in gm.graph.nodes if n.op == "call_function" and "symm_mem.fused" in str(n.target)]
+    assert retarget_symm_mem_calls(gm.graph) == 2
+    gm.graph.lint()
+    ns = torch.ops._ap_symm_mem
+    after = {n.target: str(n.args) for n in gm.graph.nodes if n.op == "call_function" and "_ap_symm_mem" in str(n.target)}
+    assert set(after) == {ns.fused_all_gather_matmul.default, ns.fused_matmul_reduce_scatter.default}
+    assert sorted(before) == sorted(after.values())              # same arguments
+    assert retarget_symm_mem_calls(gm.graph) == 0                 # idempotent
