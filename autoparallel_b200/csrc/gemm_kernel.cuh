@@ -875,7 +875,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
         // the other warps are about to reuse slots that the leader's cooperative copies may still be reading
         if (prev_coop && !coop) ptx::bulk_wait_group_read<0>();
         const long long c0 = tracing ? clock64() : 0;
-        if (p.mode == MODE_RS && own && p.ws > 1 && p.rs_arena_tma != 0) {
+        if (p.mode == MODE_RS && own && p.ws > 2 && p.rs_arena_tma != 0) {
           // the communication warps acquire the peers' flags and leave the sum of their partials
           good = smem_count_wait(sums_done, own_seen + 1u, p, abort_flag);
         } else if (p.mode == MODE_RS && own && p.ws > 1) {
@@ -941,12 +941,29 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
         // summed first, with coalesced loads (lane i takes 16-byte chunks i, i+32, ... of each
         // 4 KiB block; row-per-thread loads reached a small fraction of the memory rate). The
         // fp32 sums go through both staging buffers (8 KiB) so that each thread can pick up its row.
-        const bool own_blocked = (p.mode == MODE_RS) && own && p.ws > 1 && p.rs_arena_tma != 0;
-        if ((use_tma && !coop) || own_blocked) {
+        const bool own_any = (p.mode == MODE_RS) && own && p.ws > 1 && p.rs_arena_tma != 0;
+        // With a single peer there is nothing to sum: its bf16 partial block is added as it arrived (a pre-summed
+        // fp32 copy would cost three times the partial's bytes in extra memory traffic for a format conversion).
+        const bool own_direct = own_any && p.ws == 2;
+        const bool own_blocked = own_any && p.ws > 2;
+        if ((use_tma && !coop) || own_any) {
           // the stores that last used the staging memory must have finished reading it
           if (lane == 0) {
-            if (own_blocked) ptx::bulk_wait_group_read<0>(); else ptx::bulk_wait_group_read<1>();
+            if (own_any) ptx::bulk_wait_group_read<0>(); else ptx::bulk_wait_group_read<1>();
           }
+          __syncwarp();
+        }
+        if (own_direct) {
+          // the peer's 4 KiB block of this warp's 32 rows x 64 columns, copied as it is (rows of 128 bytes, 16-byte
+          // chunks XOR-swizzled by row, exactly as the sender staged it) into this warp's first staging slot
+          const size_t peer_stride = (size_t)sched.tiles_per_chunk * (BN / 64) * 4 * (32 * ROW_BYTES);
+          const uint8_t* pp = p.rs_arena_local + (size_t)(1 - p.rank) * peer_stride +
+                              ((((size_t)ti.tile_in_chunk * (BN / 64) + g) * 4 + quarter) * (size_t)(32 * ROW_BYTES));
+          uint4 u4[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) u4[i] = ptx::ld_cg_v4(pp + (size_t)(i * 32 + lane) * 16);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ptx::st_shared_v4(slot(0) + (uint32_t)(i * 32 + lane) * 16u, u4[i].x, u4[i].y, u4[i].z, u4[i].w);
           __syncwarp();
         }
         if (own_blocked) {
@@ -1021,7 +1038,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
             }
           }
           if (p.mode == MODE_RS && own) {
-            if (own_blocked) {
+            if (own_direct) {
+              // this thread's row of the peer's partial, half `hf`: chunk c sits at position c ^ (row & 7)
+              const uint32_t sw = (uint32_t)(lane & 7);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint32_t c = (uint32_t)(hf * 4 + j);
+                const float4 q = ptx::ld_shared_f4(slot(0) + (uint32_t)lane * (uint32_t)ROW_BYTES + ((c ^ sw) << 4));
+                const uint32_t w[4] = {__float_as_uint(q.x), __float_as_uint(q.y), __float_as_uint(q.z), __float_as_uint(q.w)};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  v[8 * j + 2 * e] += __uint_as_float(w[e] << 16);
+                  v[8 * j + 2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+                }
+              }
+            } else if (own_blocked) {
               // this thread's row of the fp32 sums, half `hf`
               const uint32_t sw = (uint32_t)(lane & 7);
 #pragma unroll
@@ -1060,7 +1091,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
           }
         }
         if (use_tma) {
-          if (own_blocked) __syncwarp();   // every lane has read its sums: the buffer may be reused
+          if (own_any) __syncwarp();   // every lane has read its sums: the buffer may be reused
           // 16-byte chunk c of this thread's row goes where the 128-byte swizzle expects it
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
@@ -1119,7 +1150,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) gemm_fused_kernel(const __grid
     __syncwarp();
   } else {
     // ============================================================ communication warps
-    if (p.mode == MODE_RS && p.ws > 1 && p.rs_arena_tma != 0) {
+    if (p.mode == MODE_RS && p.ws > 2 && p.rs_arena_tma != 0) {
       // Reduce-scatter: for every tile of this CTA that the local rank owns, wait for the peers'
       // partials, add them up block by block (coalesced 16-byte loads, two peers in flight per
       // warp) and leave the fp32 sums for the epilogue. This runs while the epilogue warps are
