@@ -240,6 +240,13 @@ bool pair_eligible(const apk::KParams& kp) {
 // the peers' row block j; and the own tiles that remain after the last partial was sent should keep the
 // tensor pipe busy for two to three waves while that partial crosses NVLink and is summed.
 int rs_lag_for(const apk::KParams& kp, long long nt, long long sched_ctas) {
+  static std::once_flag once;
+  static int forced = 0;     // APK_RS_LAG=<row blocks> in the environment overrides the rule below (tuning)
+  std::call_once(once, [] {
+    const char* e = getenv("APK_RS_LAG");
+    if (e != nullptr && atoi(e) > 0) forced = atoi(e);
+  });
+  if (forced > 0) return forced;
   const long long per_row_block = nt * (kp.ws - 1);   // peers' units per row block
   if (per_row_block <= 0 || nt <= 0) return apk::RS_LAG;
   const long long head = (3 * sched_ctas + per_row_block - 1) / per_row_block;
