@@ -233,12 +233,14 @@ bool pair_eligible(const apk::KParams& kp) {
   return mt % 2 == 0;
 }
 
-// Reduce-scatter: how many row blocks the own tiles trail the peers' (KParams::rs_lag). Two needs, both
-// in units of grid waves (measured at 8 ranks: a partial is acknowledged about 10 us after it was sent and
-// announced about 8 us later, a tile takes about 14 us): a peer's partial for row block j must be there
-// before the owner's epilogue asks for it, so row block j of the own chunk follows about three waves behind
-// the peers' row block j; and the own tiles that remain after the last partial was sent should keep the
-// tensor pipe busy for two to three waves while that partial crosses NVLink and is summed.
+// Reduce-scatter: how many row blocks the own tiles trail the peers' (KParams::rs_lag). A peer's partial for
+// row block j must be there before the owner's epilogue asks for it (measured at 8 ranks: acknowledged about
+// 10 us after it was sent, announced about 8 us later; a tile takes about 14 us), so row block j of the own chunk
+// follows about three grid waves behind the peers' row block j, and never less than the default of four row
+// blocks. Not more than that: while only peers' tiles are computed every CTA sends 64 KiB per tile (about
+// 780 GB/s per GPU, more than the fabric gives when all GPUs send) and at the end, when only own tiles are left,
+// NVLink idles, so a longer lag costs on both ends (swept at 4 ranks: 12 row blocks 1.216 ms per step, 5: 1.207,
+// 3: 1.188, same call).
 int rs_lag_for(const apk::KParams& kp, long long nt, long long sched_ctas) {
   static std::once_flag once;
   static int forced = 0;     // APK_RS_LAG=<row blocks> in the environment overrides the rule below (tuning)
@@ -248,10 +250,8 @@ int rs_lag_for(const apk::KParams& kp, long long nt, long long sched_ctas) {
   });
   if (forced > 0) return forced;
   const long long per_row_block = nt * (kp.ws - 1);   // peers' units per row block
-  if (per_row_block <= 0 || nt <= 0) return apk::RS_LAG;
-  const long long head = (3 * sched_ctas + per_row_block - 1) / per_row_block;
-  const long long tail = (5 * sched_ctas / 2 + nt - 1) / nt;
-  const long long want = head > tail ? head : tail;
+  if (per_row_block <= 0) return apk::RS_LAG;
+  const long long want = (3 * sched_ctas + per_row_block - 1) / per_row_block;
   return (int)(want > apk::RS_LAG ? want : apk::RS_LAG);
 }
 
